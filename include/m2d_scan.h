@@ -1,0 +1,117 @@
+/*
+ * m2d_scan.h -- C ABI of the B200 (sm_100a) wavefront 2-D selective scan.
+ *
+ * This is the drop-in boundary for the native side of the Mamba2D scan.  In the reference project
+ * the native boundary is a pybind11 module with two functions taking torch::Tensor by value
+ *   wf_fwd(hs, x, deltaT, deltaL, BT, BL, AT, AL)                         models/kernels/wf_cuda/wf_cuda_bind.cpp:24-34
+ *   wf_bwd(hs, x, deltaT, deltaL, AT, AL, grad_output, dDAT, dDAL, omega) models/kernels/wf_cuda/wf_cuda_bind.cpp:36-47
+ * which each run one anti-diagonal per kernel launch and leave the readout and most of the
+ * gradient arithmetic to PyTorch.  The entry points below sit one level higher, at the level of
+ * the reference's autograd Function wf_cuda_fn_pr (models/kernels/wavefront_cuda.py:146-196):
+ *   forward   (x, dT, dL, AT, AL, BT, BL, C, D)        -> y
+ *   backward  (x, dT, dL, AT, AL, BT, BL, C, D, gy)    -> nine gradients
+ * so that the 5-D hidden state never has to exist in memory.
+ *
+ * Conventions
+ *   - plain C types only; every pointer is a DEVICE pointer unless stated otherwise;
+ *   - the library never allocates or frees device memory: outputs and workspace are the caller's
+ *     (as in the reference, where Python allocates every tensor: wavefront_cuda.py:152, :181-183);
+ *   - inputs are never modified;
+ *   - calls are asynchronous on the given stream; no host synchronisation on the success path;
+ *   - every function returns M2D_OK (0) or a negative m2d_status code; m2d_strerror() names it;
+ *   - re-entrant, no global mutable state (one exception is documented where it applies).
+ */
+#ifndef M2D_SCAN_H
+#define M2D_SCAN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define M2D_ABI_VERSION 1
+
+typedef enum m2d_dtype {
+    M2D_F32 = 0,   /* float in memory, float arithmetic */
+    M2D_BF16 = 1   /* bfloat16 in memory, float arithmetic and float state */
+} m2d_dtype;
+
+typedef enum m2d_status {
+    M2D_OK = 0,
+    M2D_ERR_NULL = -1,          /* a required pointer is NULL */
+    M2D_ERR_DTYPE = -2,         /* unknown dtype */
+    M2D_ERR_SHAPE = -3,         /* B,E,N < 1, or H < 2 or W < 2 (the reference raises ValueError for
+                                   the latter: wavefront_cuda.py:322-324) */
+    M2D_ERR_UNSUPPORTED_N = -4, /* N > 16 */
+    M2D_ERR_PITCH = -5,         /* a BT/BL/C pixel pitch smaller than N */
+    M2D_ERR_WORKSPACE = -6,     /* workspace missing, too small or not 256-byte aligned */
+    M2D_ERR_LAUNCH = -7,        /* the CUDA runtime rejected a launch or a memset */
+    M2D_ERR_ABI = -8,           /* descriptor size does not match this library */
+    M2D_ERR_TOO_LARGE = -9      /* problem exceeds a fixed capacity (no-allocation entry point) */
+} m2d_status;
+
+/*
+ * Problem descriptor.  Tensor layouts are the ones the reference op receives:
+ *   x, dT, dL, y, gy, d_x, d_dT, d_dL   (B,H,W,E) contiguous, channels last
+ *   AT, AL, d_AT, d_AL                  (E,N) contiguous; A = -exp(A_log) already applied
+ *   D, d_D                              (E)
+ *   BT, BL, C                           (B,H,W,N) with unit stride over N and a per-tensor pixel
+ *                                       pitch in ELEMENTS (row stride W*pitch, batch stride
+ *                                       H*W*pitch).  The reference produces these as views into
+ *                                       one projection output with pitch 2R+3N
+ *                                       (wavefront_cuda.py:78-82); a contiguous tensor has pitch N.
+ *   d_BT, d_BL, d_C                     (B,H,W,N) contiguous
+ * All tensors share `dtype`.
+ */
+typedef struct m2d_scan_desc {
+    uint32_t struct_bytes;      /* = sizeof(m2d_scan_desc) */
+    int32_t dtype;              /* m2d_dtype */
+    int32_t B, H, W, E, N;
+    int32_t reserved0;
+    const void *x, *dT, *dL;
+    const void *AT, *AL;
+    const void *BT, *BL, *C;
+    int64_t BT_pitch, BL_pitch, C_pitch;
+    const void *D;
+    void *y;                    /* forward output */
+    const void *gy;             /* backward input: upstream gradient of y */
+    void *d_x, *d_dT, *d_dL, *d_AT, *d_AL, *d_BT, *d_BL, *d_C, *d_D;   /* backward outputs */
+    void *workspace;            /* scratch, 256-byte aligned, see *_workspace() */
+    uint64_t workspace_bytes;
+} m2d_scan_desc;
+
+/* ABI version of the loaded library (compare with M2D_ABI_VERSION). */
+int m2d_abi_version(void);
+
+/* Static string naming a status code. */
+const char *m2d_strerror(int status);
+
+/*
+ * Bytes of scratch m2d_scan_fwd / m2d_scan_bwd need for this problem on the current device
+ * (0 is possible).  Replaces the reference's Python-side allocations of hs / dDAT / dDAL / omega
+ * (wavefront_cuda.py:152, :181-183).  Returns 0 for an invalid descriptor.
+ */
+uint64_t m2d_scan_fwd_workspace(const m2d_scan_desc *desc);
+uint64_t m2d_scan_bwd_workspace(const m2d_scan_desc *desc);
+
+/*
+ * Forward: y = sum_n h*C + x*D with h the two-neighbour recurrence.
+ * Replaces wf_fwd (wf_cuda_bind.cpp:24-34) + the readout (wavefront_cuda.py:156).
+ * Reads x,dT,dL,AT,AL,BT,BL,C,D; writes y; uses workspace.  `stream` is a cudaStream_t.
+ */
+int m2d_scan_fwd(const m2d_scan_desc *desc, void *stream);
+
+/*
+ * Backward with recomputation of the hidden state: all nine gradients of the forward.
+ * Replaces the body of wf_cuda_fn_pr.backward (wavefront_cuda.py:163-196): the recompute of hs,
+ * wf_bwd (wf_cuda_bind.cpp:36-47) and fused_backward_math (wavefront_cuda.py:97-139).
+ * Reads the forward inputs and gy; writes d_x..d_D; uses workspace.
+ */
+int m2d_scan_bwd(const m2d_scan_desc *desc, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* M2D_SCAN_H */

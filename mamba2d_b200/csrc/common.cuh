@@ -1,0 +1,111 @@
+// Shared device helpers and the launch plan for the sm_100a wavefront-scan kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "m2d_scan.h"
+
+namespace m2d {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr int kGroup = 32;      // channels owned by one warp (8 lanes x 4 channels)
+constexpr int kMaxN = 16;       // states owned by one warp   (4 lanes x 4 states)
+constexpr int kSlotF4 = 128;    // float4 per (cell, warp) state record: 4 quads x 32 lanes
+
+// Thread layout inside a warp.  A warp owns 32 channels x 16 states of one pixel; lane = (cq, nq)
+// owns the 4x4 block channels [4cq, 4cq+4) x states [4nq, 4nq+4).  Sums over states finish with a
+// 2-step exchange across the 4 nq lanes, sums over channels with a 3-step exchange across cq.
+
+__device__ __forceinline__ float ex2(float v) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// ---- element loads: four consecutive elements as floats, zero beyond `nvalid` ----------------
+template <bool VEC>
+__device__ __forceinline__ float4 load4(const float* __restrict__ p, long long off, int nvalid) {
+    if (VEC) return __ldg(reinterpret_cast<const float4*>(p + off));
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (nvalid > 0) r.x = __ldg(p + off);
+    if (nvalid > 1) r.y = __ldg(p + off + 1);
+    if (nvalid > 2) r.z = __ldg(p + off + 2);
+    if (nvalid > 3) r.w = __ldg(p + off + 3);
+    return r;
+}
+__device__ __forceinline__ float bf16_bits_to_float(unsigned short b) { return __uint_as_float(static_cast<unsigned>(b) << 16); }
+template <bool VEC>
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* __restrict__ p, long long off, int nvalid) {
+    if (VEC) {
+        const uint2 u = __ldg(reinterpret_cast<const uint2*>(p + off));
+        return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                           __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+    }
+    const unsigned short* q = reinterpret_cast<const unsigned short*>(p) + off;
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (nvalid > 0) r.x = bf16_bits_to_float(__ldg(q));
+    if (nvalid > 1) r.y = bf16_bits_to_float(__ldg(q + 1));
+    if (nvalid > 2) r.z = bf16_bits_to_float(__ldg(q + 2));
+    if (nvalid > 3) r.w = bf16_bits_to_float(__ldg(q + 3));
+    return r;
+}
+__device__ __forceinline__ float load1(const float* __restrict__ p, long long off) { return __ldg(p + off); }
+__device__ __forceinline__ float load1(const __nv_bfloat16* __restrict__ p, long long off) {
+    return bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(p) + off));
+}
+__device__ __forceinline__ void store1(float* p, long long off, float v) { p[off] = v; }
+__device__ __forceinline__ void store1(__nv_bfloat16* p, long long off, float v) { p[off] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float sel4(const float4& v, int k) {
+    return k == 0 ? v.x : (k == 1 ? v.y : (k == 2 ? v.z : v.w));
+}
+
+// Sum four per-channel partials over the 4 nq lanes.  On return lane nq holds the total of
+// channel index nq of its 4-channel block (so lane l of the warp holds channel l of the group).
+__device__ __forceinline__ float reduce_states(float v0, float v1, float v2, float v3, int nq) {
+    const bool hi2 = (nq & 2) != 0;
+    float k0 = hi2 ? v2 : v0, k1 = hi2 ? v3 : v1;
+    const float s0 = hi2 ? v0 : v2, s1 = hi2 ? v1 : v3;
+    k0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+    k1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    const bool hi1 = (nq & 1) != 0;
+    const float k = hi1 ? k1 : k0, s = hi1 ? k0 : k1;
+    return k + __shfl_xor_sync(0xffffffffu, s, 1);
+}
+
+// Cell position inside a CTA's work list.  A CTA walks `nb` images; each image is cut into
+// `nbands` bands of `Rb` rows; warp r of the CTA owns row q*Rb + r of band q and walks its W
+// columns, one per step, lagging r steps behind warp 0 so that the row above is always one step
+// ahead (the anti-diagonal wavefront).
+struct Pos {
+    int j, q, bi;
+};
+__device__ __forceinline__ Pos advance(Pos a, int W, int nbands) {
+    if (++a.j == W) {
+        a.j = 0;
+        if (++a.q == nbands) { a.q = 0; ++a.bi; }
+    }
+    return a;
+}
+
+// Host-side launch plan shared by the workspace queries and the launches.
+struct Plan {
+    int groups;        // ceil(E / 32)
+    int warps;         // row-warps per CTA
+    int Rb;            // rows per band (<= warps)
+    int nbands;        // ceil(H / Rb)
+    int grid_x;        // CTAs per channel group; each walks images blockIdx.x, +grid_x, ...
+    size_t smem;       // dynamic shared memory per CTA
+    size_t scratch;    // workspace bytes
+};
+
+}  // namespace m2d

@@ -1,0 +1,66 @@
+// Forward entry point of the wavefront scan: one fused kernel, y written directly.
+#include "plan.cuh"
+#include "sweep_fwd.cuh"
+
+namespace m2d {
+
+template <typename io_t, bool VEC>
+__global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
+    extern __shared__ float4 handoff[];
+    const int lane = threadIdx.x & 31;
+    const int cq = lane >> 2, nq = lane & 3;
+    const int g = blockIdx.y;
+    const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
+    const int chv = min(4, max(0, a.E - ch0));
+    const int nv = min(4, max(0, a.N - n0));
+
+    const int total = 2 * ((blockDim.x >> 5) + 1) * kSlotF4;
+    for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    float aT2[4][4], aL2[4][4];
+    load_param_block<io_t>(aT2, a.AT, a.N, ch0, chv, n0, nv, kLog2e);
+    load_param_block<io_t>(aL2, a.AL, a.N, ch0, chv, n0, nv, kLog2e);
+    const int ch_own = g * kGroup + lane;
+    const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
+    __syncthreads();
+
+    const int nb = (a.B - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    forward_sweep<io_t, VEC, false>(a, handoff, aT2, aL2, D_own, blockIdx.x, gridDim.x, nb);
+}
+
+template <typename io_t>
+static int launch_fwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStream_t st) {
+    FwdArgs a;
+    a.B = d->B; a.H = d->H; a.W = d->W; a.E = d->E; a.N = d->N;
+    a.x = d->x; a.dT = d->dT; a.dL = d->dL; a.AT = d->AT; a.AL = d->AL;
+    a.BT = d->BT; a.BL = d->BL; a.C = d->C; a.D = d->D;
+    a.pBT = d->BT_pitch; a.pBL = d->BL_pitch; a.pC = d->C_pitch;
+    a.y = d->y;
+    a.ring = static_cast<float4*>(d->workspace);
+    a.hs = nullptr;
+    a.Rb = pl.Rb; a.nbands = pl.nbands;
+    dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
+    if (vec) m2d_fwd_kernel<io_t, true><<<grid, block, pl.smem, st>>>(a);
+    else m2d_fwd_kernel<io_t, false><<<grid, block, pl.smem, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
+}
+
+}  // namespace m2d
+
+extern "C" uint64_t m2d_scan_fwd_workspace(const m2d_scan_desc* d) {
+    if (m2d::check_desc(d, false, false) != M2D_OK) return 0;
+    return m2d::plan_fwd(d).scratch;
+}
+
+extern "C" int m2d_scan_fwd(const m2d_scan_desc* d, void* stream) {
+    int rc = m2d::check_desc(d, false, true);
+    if (rc != M2D_OK) return rc;
+    if (!d->y) return M2D_ERR_NULL;
+    const m2d::Plan pl = m2d::plan_fwd(d);
+    if (pl.scratch > 0 && (!d->workspace || d->workspace_bytes < pl.scratch || (reinterpret_cast<uintptr_t>(d->workspace) & 255)))
+        return M2D_ERR_WORKSPACE;
+    const bool vec = m2d::vector_ok(d, false);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (d->dtype == M2D_F32) return m2d::launch_fwd<float>(d, pl, vec, st);
+    return m2d::launch_fwd<__nv_bfloat16>(d, pl, vec, st);
+}

@@ -1,0 +1,271 @@
+"""Drop-in replacement for the reference's ``models/kernels/wavefront_cuda.py``.
+
+Same public names and call signatures as the reference module, so ``models/mamba2d.py`` (and the
+copy under ``downstream/Mamba2D``) can import this module in its place unchanged:
+
+  wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b,
+                      D, recomp="partial")                      reference: wavefront_cuda.py:315-347
+  wf_cuda_fn_pr.apply(x, deltaT, deltaL, AT, AL, BT, BL, C, D)   reference: wavefront_cuda.py:146-196
+  wf_cuda_fn_fr.apply(x, AT_log, AL_log, x_proj_w, ..., D)       reference: wavefront_cuda.py:199-313
+  proj_params(x, AT_log, AL_log, x_proj_w, ...)                  reference: wavefront_cuda.py:63-95
+
+What differs underneath: the reference launches one kernel per anti-diagonal, materialises the 5-D
+hidden state and finishes the readout and the gradient arithmetic in PyTorch.  Here the forward and
+the backward are one fused sm_100a kernel each, reached through the C ABI in ``include/m2d_scan.h``.
+There is no PyTorch or CPU fallback: tensors must live on a CUDA device and the prebuilt library
+must be present, otherwise a ``RuntimeError`` is raised.
+"""
+import ctypes
+
+import torch
+import torch.library
+import torch.nn.functional as F
+
+from . import _lib
+
+__all__ = ["wavefront_scan_cuda", "wf_cuda_fn_pr", "wf_cuda_fn_fr", "proj_params", "scan_fwd", "scan_bwd"]
+
+_DTYPES = {torch.float32: _lib.M2D_F32, torch.bfloat16: _lib.M2D_BF16}
+
+
+# -----------------------------------------------------------------------------
+# Descriptor plumbing
+# -----------------------------------------------------------------------------
+
+def _pixel_pitch(t, H, W, N):
+    """Return (tensor, pitch) with ``tensor`` laid out as (B,H,W,N) rows of ``pitch`` elements.
+
+    Views into a wider (B,H,W,K) buffer -- what ``proj_params`` returns for BT, BL, C -- are passed
+    through untouched; anything else is made contiguous."""
+    s = t.stride()
+    K = s[2]
+    if s[3] == 1 and K >= N and s[1] == W * K and s[0] == H * W * K:
+        return t, K
+    return t.contiguous(), N
+
+
+def _check_inputs(x, dT, dL, AT, AL, BT, BL, C, D, gy=None):
+    if x.dim() != 4:
+        raise RuntimeError(f"x must be (B,H,W,E), got {tuple(x.shape)}")
+    if not x.is_cuda:
+        raise RuntimeError("wavefront scan: tensors must be on a CUDA device (there is no CPU path)")
+    if x.dtype not in _DTYPES:
+        raise RuntimeError(f"wavefront scan: unsupported dtype {x.dtype} (float32 and bfloat16 only)")
+    B, H, W, E = x.shape
+    if AT.dim() != 2 or AT.shape[0] != E:
+        raise RuntimeError(f"AT must be (E,N) with E={E}, got {tuple(AT.shape)}")
+    N = AT.shape[1]
+    want = {"deltaT": (dT, (B, H, W, E)), "deltaL": (dL, (B, H, W, E)), "AL": (AL, (E, N)),
+            "BT": (BT, (B, H, W, N)), "BL": (BL, (B, H, W, N)), "C": (C, (B, H, W, N)), "D": (D, (E,))}
+    if gy is not None:
+        want["grad_output"] = (gy, (B, H, W, E))
+    for name, (t, shape) in want.items():
+        if tuple(t.shape) != shape:
+            raise RuntimeError(f"{name} must have shape {shape}, got {tuple(t.shape)}")
+    for name, t in [("x", x), ("AT", AT)] + [(k, v[0]) for k, v in want.items()]:
+        if t.dtype != x.dtype:
+            raise RuntimeError(f"{name} has dtype {t.dtype}, expected {x.dtype}")
+        if t.device != x.device:
+            raise RuntimeError(f"{name} is on {t.device}, expected {x.device}")
+    return B, H, W, E, N
+
+
+def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D):
+    B, H, W, E = x.shape
+    N = AT.shape[1]
+    keep = []   # tensors that must outlive the launch call
+    d = _lib.ScanDesc()
+    d.struct_bytes = ctypes.sizeof(_lib.ScanDesc)
+    d.dtype = _DTYPES[x.dtype]
+    d.B, d.H, d.W, d.E, d.N = B, H, W, E, N
+    for name, t in (("x", x), ("dT", dT), ("dL", dL), ("AT", AT), ("AL", AL), ("D", D)):
+        t = t.contiguous()
+        keep.append(t)
+        setattr(d, name, t.data_ptr())
+    for name, t in (("BT", BT), ("BL", BL), ("C", C)):
+        t, pitch = _pixel_pitch(t, H, W, N)
+        keep.append(t)
+        setattr(d, name, t.data_ptr())
+        setattr(d, name + "_pitch", pitch)
+    return d, keep
+
+
+def _workspace(d, nbytes, device, keep):
+    if nbytes:
+        ws = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+        keep.append(ws)
+        d.workspace = ws.data_ptr()
+        d.workspace_bytes = int(nbytes)
+
+
+def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D):
+    """Fused forward: y (B,H,W,E) in ``x.dtype``.  Inputs as ``wf_cuda_fn_pr.apply`` takes them."""
+    _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        d.y = y.data_ptr()
+        _workspace(d, L.m2d_scan_fwd_workspace(ctypes.byref(d)), x.device, keep)
+        rc = L.m2d_scan_fwd(ctypes.byref(d), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(rc, "m2d_scan_fwd")
+    return y
+
+
+def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output):
+    """Fused backward with recomputation.  Returns the nine gradients
+    (d_x, d_deltaT, d_deltaL, d_AT, d_AL, d_BT, d_BL, d_C, d_D), all in ``x.dtype``."""
+    B, H, W, E, N = _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output)
+    L = _lib.lib()
+    dev, dt = x.device, x.dtype
+    with torch.cuda.device(dev):
+        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        gy = grad_output.contiguous()
+        keep.append(gy)
+        d.gy = gy.data_ptr()
+        outs = (torch.empty((B, H, W, E), dtype=dt, device=dev), torch.empty((B, H, W, E), dtype=dt, device=dev),
+                torch.empty((B, H, W, E), dtype=dt, device=dev), torch.empty((E, N), dtype=dt, device=dev),
+                torch.empty((E, N), dtype=dt, device=dev), torch.empty((B, H, W, N), dtype=dt, device=dev),
+                torch.empty((B, H, W, N), dtype=dt, device=dev), torch.empty((B, H, W, N), dtype=dt, device=dev),
+                torch.empty((E,), dtype=dt, device=dev))
+        for name, t in zip(("d_x", "d_dT", "d_dL", "d_AT", "d_AL", "d_BT", "d_BL", "d_C", "d_D"), outs):
+            setattr(d, name, t.data_ptr())
+        _workspace(d, L.m2d_scan_bwd_workspace(ctypes.byref(d)), dev, keep)
+        rc = L.m2d_scan_bwd(ctypes.byref(d), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(rc, "m2d_scan_bwd")
+    return outs
+
+
+# -----------------------------------------------------------------------------
+# Custom operators (opaque to torch.compile; the reference registers mamba2d::wf_fwd / wf_bwd,
+# wavefront_cuda.py:25-57)
+# -----------------------------------------------------------------------------
+
+@torch.library.custom_op("mamba2d_b200::scan_fwd", mutates_args=())
+def scan_fwd_op(x: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, AT: torch.Tensor, AL: torch.Tensor,
+                BT: torch.Tensor, BL: torch.Tensor, C: torch.Tensor, D: torch.Tensor) -> torch.Tensor:
+    return scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+
+
+@scan_fwd_op.register_fake
+def _scan_fwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op("mamba2d_b200::scan_bwd", mutates_args=())
+def scan_bwd_op(x: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, AT: torch.Tensor, AL: torch.Tensor,
+                BT: torch.Tensor, BL: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
+                grad_output: torch.Tensor) -> list[torch.Tensor]:
+    return list(scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output))
+
+
+@scan_bwd_op.register_fake
+def _scan_bwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output):
+    B, H, W, E = x.shape
+    N = AT.shape[1]
+    mk = lambda *s: x.new_empty(s)
+    return [mk(B, H, W, E), mk(B, H, W, E), mk(B, H, W, E), mk(E, N), mk(E, N),
+            mk(B, H, W, N), mk(B, H, W, N), mk(B, H, W, N), mk(E)]
+
+
+# -----------------------------------------------------------------------------
+# Projections (plain PyTorch on both sides of the comparison; cuBLAS GEMMs)
+# -----------------------------------------------------------------------------
+
+def proj_params(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
+    """Input-dependent scan parameters from x (B,H,W,E).
+
+    Returns deltaT, deltaL (B,H,W,E), AT, AL (E,N), BT, BL, C (B,H,W,N), all in ``x.dtype``;
+    BT/BL/C are views into the x-projection output (pixel pitch 2R+3N), which the kernels read
+    in place."""
+    d_state = AT_log.shape[1]
+    dt_rank = dt_projT_w.shape[1]
+    AT = -torch.exp(AT_log.float())
+    AL = -torch.exp(AL_log.float())
+    delta2BC = F.linear(x, x_proj_w)
+    rT, rL, BT, BL, C = torch.split(delta2BC, [dt_rank, dt_rank, d_state, d_state, d_state], dim=-1)
+    deltaT = F.softplus(F.linear(rT, dt_projT_w, dt_projT_b))
+    deltaL = F.softplus(F.linear(rL, dt_projL_w, dt_projL_b))
+    dt = x.dtype
+    return (deltaT.to(dtype=dt), deltaL.to(dtype=dt), AT.to(dtype=dt), AL.to(dtype=dt),
+            BT.to(dtype=dt), BL.to(dtype=dt), C.to(dtype=dt))
+
+
+# -----------------------------------------------------------------------------
+# Autograd Functions
+# -----------------------------------------------------------------------------
+
+class wf_cuda_fn_pr(torch.autograd.Function):
+    """Partial recomputation: projections are computed once and saved; the hidden state is
+    recomputed inside the backward kernel."""
+
+    @staticmethod
+    def forward(ctx, x, deltaT, deltaL, AT, AL, BT, BL, C, D):
+        y = scan_fwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        ctx.save_for_backward(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, deltaT, deltaL, AT, AL, BT, BL, C, D = ctx.saved_tensors
+        grads = scan_bwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output.to(x.dtype))
+        return tuple(grads)
+
+
+class wf_cuda_fn_fr(torch.autograd.Function):
+    """Full recomputation: only x and the weights are saved; the projections are recomputed (with
+    an autograd graph) in backward, as in the reference."""
+
+    @staticmethod
+    def forward(ctx, x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D):
+        with torch.no_grad():
+            deltaT, deltaL, AT, AL, BT, BL, C = proj_params(
+                x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
+        y = scan_fwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        ctx.save_for_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D = ctx.saved_tensors
+        grad_output = grad_output.to(x.dtype)
+        with torch.enable_grad():
+            leaves = [t.detach().requires_grad_(True) for t in
+                      (x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)]
+            proj = proj_params(*leaves)
+        deltaT, deltaL, AT, AL, BT, BL, C = (t.detach() for t in proj)
+        d_x_scan, d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C, d_D = scan_bwd_op(
+            x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output)
+        # proj returns (deltaT, deltaL, AT, AL, BT, BL, C)
+        g = torch.autograd.grad(list(proj), leaves, [d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C], retain_graph=False)
+        d_x = d_x_scan + g[0]
+        return (d_x, *g[1:], d_D)
+
+
+def wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, recomp="partial"):
+    """The op as ``M2DBlock.ssm`` calls it.
+
+    Args:
+        recomp: ``"partial"`` saves the projections for backward; ``"full"`` saves only x and the
+            weights and recomputes the projections in backward (less memory, slower).
+    Raises:
+        ValueError: if H < 2 or W < 2, or for an unknown ``recomp`` (same conditions as the reference).
+    """
+    _, H, W, _ = x.shape
+    if H < 2 or W < 2:
+        raise ValueError(f"Wavefront scan kernel requires spatial dims > 1. Got H={H}, W={W}.")
+
+    x_proj_w = x_proj_w.to(x.dtype)
+    dt_projT_w = dt_projT_w.to(x.dtype)
+    dt_projT_b = dt_projT_b.to(x.dtype)
+    dt_projL_w = dt_projL_w.to(x.dtype)
+    dt_projL_b = dt_projL_b.to(x.dtype)
+    D = D.to(x.dtype)
+
+    if recomp == "partial":
+        deltaT, deltaL, AT, AL, BT, BL, C = proj_params(
+            x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
+        return wf_cuda_fn_pr.apply(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+    if recomp == "full":
+        return wf_cuda_fn_fr.apply(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D)
+    raise ValueError(f"Unknown recomputation mode, got {recomp}...")
