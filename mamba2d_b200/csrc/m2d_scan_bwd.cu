@@ -1,3 +1,187 @@
+// Backward entry point of the wavefront scan: recompute sweep + adjoint sweep in one kernel,
+// followed by a small kernel that casts the fp32 accumulators of the reduced gradients.
 #include "plan.cuh"
-extern "C" uint64_t m2d_scan_bwd_workspace(const m2d_scan_desc* d) { (void)d; return 0; }
-extern "C" int m2d_scan_bwd(const m2d_scan_desc* d, void* stream) { (void)d; (void)stream; return M2D_ERR_LAUNCH; }
+#include "sweep_bwd.cuh"
+
+namespace m2d {
+
+// Workspace layout of the backward pass (all regions 256-byte aligned):
+//   hs     state record written by the recompute sweep     B*groups*H*W*2 KiB
+//   ring   per-CTA band-boundary ring                      ctas*W*2 KiB   (only if nbands > 1)
+//   acc    fp32 accumulators: [B*H*W][48] | [2][E][N] | [E]   (zeroed before the main kernel)
+struct BwdLayout {
+    size_t hs, ring, accBC, accA, accD, total, acc_begin;
+};
+
+inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
+    BwdLayout L;
+    size_t off = 0;
+    L.hs = off;
+    off += align256((size_t)d->B * p.groups * d->H * d->W * kSlotF4 * sizeof(float4));
+    L.ring = off;
+    if (p.nbands > 1) off += align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
+    L.acc_begin = off;
+    L.accBC = off;
+    off += align256((size_t)d->B * d->H * d->W * 48 * sizeof(float));
+    L.accA = off;
+    off += align256((size_t)2 * d->E * d->N * sizeof(float));
+    L.accD = off;
+    off += align256((size_t)d->E * sizeof(float));
+    L.total = off;
+    return L;
+}
+
+inline Plan plan_bwd(const m2d_scan_desc* d) {
+    Plan p = plan_common(d, 8, 1);
+    p.scratch = bwd_layout(d, p).total;
+    return p;
+}
+
+template <typename io_t, bool VEC>
+__global__ void __launch_bounds__(256, 1) m2d_bwd_kernel(const ScanArgs a) {
+    extern __shared__ float4 handoff[];
+    const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
+    const int cq = lane >> 2, nq = lane & 3;
+    const int g = blockIdx.y;
+    const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
+    const int chv = min(4, max(0, a.E - ch0));
+    const int nv = min(4, max(0, a.N - n0));
+
+    const int total = 2 * (nwarps + 1) * kSlotF4;
+    for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    float aT2[4][4], aL2[4][4];
+    load_param_block<io_t>(aT2, a.AT, a.N, ch0, chv, n0, nv, kLog2e);
+    load_param_block<io_t>(aL2, a.AL, a.N, ch0, chv, n0, nv, kLog2e);
+    const int ch_own = g * kGroup + lane;
+    const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
+    float dAT[4][4], dAL[4][4], dD[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        dD[c] = 0.f;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) dAT[c][n] = dAL[c][n] = 0.f;
+    }
+    __syncthreads();
+
+    for (int b = blockIdx.x; b < a.B; b += gridDim.x) {
+        forward_sweep<io_t, VEC, true>(a, handoff, aT2, aL2, D_own, b, 0, 1);
+        reverse_sweep<io_t, VEC>(a, handoff, aT2, aL2, D_own, dAT, dAL, dD, b);
+    }
+
+    // ---- per-(channel,state) sums: fold the CTA's row-warps through shared memory, then one
+    //      atomic per value from warp 0 ----------------------------------------------------------
+    float* red = reinterpret_cast<float*>(handoff);     // reuse: needs 36 floats per thread
+    const int slot = 2 * (nwarps + 1) * kSlotF4 * 4;     // floats available
+    const bool fits = (int)blockDim.x * 36 <= slot;
+    if (fits && nwarps > 1) {
+        float* mine = red + (size_t)threadIdx.x * 36;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int n = 0; n < 4; ++n) { mine[c * 4 + n] = dAT[c][n]; mine[16 + c * 4 + n] = dAL[c][n]; }
+            mine[32 + c] = dD[c];
+        }
+        __syncthreads();
+        if (r == 0) {
+            for (int w = 1; w < nwarps; ++w) {
+                const float* o = red + (size_t)(w * 32 + lane) * 36;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int n = 0; n < 4; ++n) { dAT[c][n] += o[c * 4 + n]; dAL[c][n] += o[16 + c * 4 + n]; }
+                    dD[c] += o[32 + c];
+                }
+            }
+        }
+    }
+    if (r == 0 || !(fits && nwarps > 1)) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (c < chv) {
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    if (n < nv) {
+                        atomicAdd(a.accA + (size_t)(ch0 + c) * a.N + n0 + n, dAT[c][n]);
+                        atomicAdd(a.accA + (size_t)a.E * a.N + (size_t)(ch0 + c) * a.N + n0 + n, dAL[c][n]);
+                    }
+                }
+                if (nq == 0) atomicAdd(a.accD + ch0 + c, dD[c]);
+            }
+        }
+    }
+}
+
+// Cast the fp32 accumulators into the caller's gradient tensors.
+template <typename io_t>
+__global__ void m2d_bwd_finalize(const float* __restrict__ accBC, const float* __restrict__ accA, const float* __restrict__ accD,
+                                 io_t* d_BT, io_t* d_BL, io_t* d_C, io_t* d_AT, io_t* d_AL, io_t* d_D,
+                                 long long npix, int N, int E) {
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long nthreads = (long long)gridDim.x * blockDim.x;
+    const long long tot = npix * N;
+    for (long long k = tid; k < tot; k += nthreads) {
+        const long long p = k / N;
+        const int n = (int)(k - p * N);
+        store1(d_BT, k, accBC[p * 48 + n]);
+        store1(d_BL, k, accBC[p * 48 + 16 + n]);
+        store1(d_C, k, accBC[p * 48 + 32 + n]);
+    }
+    for (long long k = tid; k < (long long)E * N; k += nthreads) {
+        store1(d_AT, k, accA[k]);
+        store1(d_AL, k, accA[(long long)E * N + k]);
+    }
+    for (long long k = tid; k < E; k += nthreads) store1(d_D, k, accD[k]);
+}
+
+template <typename io_t>
+static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStream_t st) {
+    const BwdLayout L = bwd_layout(d, pl);
+    char* ws = static_cast<char*>(d->workspace);
+    ScanArgs a;
+    a.B = d->B; a.H = d->H; a.W = d->W; a.E = d->E; a.N = d->N;
+    a.x = d->x; a.dT = d->dT; a.dL = d->dL; a.AT = d->AT; a.AL = d->AL;
+    a.BT = d->BT; a.BL = d->BL; a.C = d->C; a.D = d->D;
+    a.pBT = d->BT_pitch; a.pBL = d->BL_pitch; a.pC = d->C_pitch;
+    a.y = nullptr;
+    a.ring = reinterpret_cast<float4*>(ws + L.ring);
+    a.Rb = pl.Rb; a.nbands = pl.nbands;
+    a.gy = d->gy;
+    a.hs = reinterpret_cast<float4*>(ws + L.hs);
+    a.accBC = reinterpret_cast<float*>(ws + L.accBC);
+    a.accA = reinterpret_cast<float*>(ws + L.accA);
+    a.accD = reinterpret_cast<float*>(ws + L.accD);
+    a.d_x = d->d_x; a.d_dT = d->d_dT; a.d_dL = d->d_dL;
+    if (cudaMemsetAsync(ws + L.acc_begin, 0, L.total - L.acc_begin, st) != cudaSuccess) return M2D_ERR_LAUNCH;
+    dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
+    if (vec) m2d_bwd_kernel<io_t, true><<<grid, block, pl.smem, st>>>(a);
+    else m2d_bwd_kernel<io_t, false><<<grid, block, pl.smem, st>>>(a);
+    if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
+    const long long npix = (long long)d->B * d->H * d->W;
+    const int fin_blocks = (int)((npix * d->N + 255) / 256 < 148 * 8 ? (npix * d->N + 255) / 256 : 148 * 8);
+    m2d_bwd_finalize<io_t><<<fin_blocks, 256, 0, st>>>(a.accBC, a.accA, a.accD, static_cast<io_t*>(d->d_BT),
+                                                      static_cast<io_t*>(d->d_BL), static_cast<io_t*>(d->d_C),
+                                                      static_cast<io_t*>(d->d_AT), static_cast<io_t*>(d->d_AL),
+                                                      static_cast<io_t*>(d->d_D), npix, d->N, d->E);
+    return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
+}
+
+}  // namespace m2d
+
+extern "C" uint64_t m2d_scan_bwd_workspace(const m2d_scan_desc* d) {
+    if (m2d::check_desc(d, true, false) != M2D_OK) return 0;
+    return m2d::plan_bwd(d).scratch;
+}
+
+extern "C" int m2d_scan_bwd(const m2d_scan_desc* d, void* stream) {
+    int rc = m2d::check_desc(d, true, true);
+    if (rc != M2D_OK) return rc;
+    const m2d::Plan pl = m2d::plan_bwd(d);
+    if (!d->workspace || d->workspace_bytes < pl.scratch || (reinterpret_cast<uintptr_t>(d->workspace) & 255))
+        return M2D_ERR_WORKSPACE;
+    const bool vec = m2d::vector_ok(d, true);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (d->dtype == M2D_F32) return m2d::launch_bwd<float>(d, pl, vec, st);
+    return m2d::launch_bwd<__nv_bfloat16>(d, pl, vec, st);
+}

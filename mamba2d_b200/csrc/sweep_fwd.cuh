@@ -20,23 +20,32 @@
 
 namespace m2d {
 
-struct FwdArgs {
+struct ScanArgs {
     int B, H, W, E, N;
     const void *x, *dT, *dL, *AT, *AL, *BT, *BL, *C, *D;
     long long pBT, pBL, pC;   // pixel pitch (elements) of BT, BL, C
     void* y;
     float4* ring;             // per-CTA band-boundary ring: [cta][W][4][32] float4
-    float4* hs;               // optional full state record: [b][group][H*W][4][32] float4 (backward only)
     int Rb, nbands;
+    // ---- backward only ----
+    const void* gy;
+    float4* hs;               // full state record: [b][group][H*W][4][32] float4
+    float* accBC;             // fp32 accumulators [B*H*W][48]: d_BT | d_BL | d_C
+    float* accA;              // fp32 accumulators [2][E][N]:   d_AT | d_AL
+    float* accD;              // fp32 accumulators [E]
+    void *d_x, *d_dT, *d_dL;
 };
+typedef ScanArgs FwdArgs;
 
 // Cell inputs held in registers (current step and the prefetched next step).
 struct CellIn {
     float4 x, dT, dL, bT, bL, c;
+    float4 gy;   // only loaded by the backward sweeps
 };
 
-template <typename io_t, bool VEC>
+template <typename io_t, bool VEC, bool WITH_GY>
 __device__ __forceinline__ void load_cell(CellIn& ci, const FwdArgs& a, long long pix, int ch0, int chv, int n0, int nv) {
+    if (WITH_GY) ci.gy = load4<VEC>(static_cast<const io_t*>(a.gy), pix * a.E + ch0, chv);
     ci.x = load4<VEC>(static_cast<const io_t*>(a.x), pix * a.E + ch0, chv);
     ci.dT = load4<VEC>(static_cast<const io_t*>(a.dT), pix * a.E + ch0, chv);
     ci.dL = load4<VEC>(static_cast<const io_t*>(a.dL), pix * a.E + ch0, chv);
@@ -87,8 +96,8 @@ __device__ __forceinline__ void forward_sweep(const FwdArgs& a, float4* handoff,
     Pos pn = {0, 0, 0};
     bool vn = (r == 0) && (r < Rb) && (nb > 0);
     CellIn nxt;
-    nxt.x = nxt.dT = nxt.dL = nxt.bT = nxt.bL = nxt.c = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (vn) load_cell<io_t, VEC>(nxt, a, (long long)img0 * H * W, ch0, chv, n0, nv);
+    nxt.x = nxt.dT = nxt.dL = nxt.bT = nxt.bL = nxt.c = nxt.gy = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (vn) load_cell<io_t, VEC, STORE_HS>(nxt, a, (long long)img0 * H * W, ch0, chv, n0, nv);
 
     for (int s = 0; s < steps; ++s) {
         const Pos pc = pn;
@@ -103,7 +112,7 @@ __device__ __forceinline__ void forward_sweep(const FwdArgs& a, float4* handoff,
         if (vn) {
             const int bn = img0 + pn.bi * img_stride;
             const long long pix = ((long long)bn * H + (pn.q * Rb + r)) * W + pn.j;
-            load_cell<io_t, VEC>(nxt, a, pix, ch0, chv, n0, nv);
+            load_cell<io_t, VEC, STORE_HS>(nxt, a, pix, ch0, chv, n0, nv);
             if (r == 0 && pn.q > 0) {
                 // row above lives in the previous band: pull it from the ring into slot 0
 #pragma unroll
@@ -133,6 +142,8 @@ __device__ __forceinline__ void forward_sweep(const FwdArgs& a, float4* handoff,
             const float bLs[4] = {cur.bL.x, cur.bL.y, cur.bL.z, cur.bL.w};
             const float cs[4] = {cur.c.x, cur.c.y, cur.c.z, cur.c.w};
             float yacc[4];
+            float dC[4] = {0.f, 0.f, 0.f, 0.f};   // backward only: sum over this thread's channels of gy*h
+            const float gys[4] = {cur.gy.x, cur.gy.y, cur.gy.z, cur.gy.w};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float tp[4] = {top[c].x, top[c].y, top[c].z, top[c].w};
@@ -147,6 +158,7 @@ __device__ __forceinline__ void forward_sweep(const FwdArgs& a, float4* handoff,
                     const float hn = fmaf(gL, h[c][n], fmaf(gT, tp[n], u));
                     h[c][n] = hn;
                     acc = fmaf(hn, cs[n], acc);
+                    if (STORE_HS) dC[n] = fmaf(gys[c], hn, dC[n]);
                 }
                 yacc[c] = acc;
             }
@@ -161,6 +173,20 @@ __device__ __forceinline__ void forward_sweep(const FwdArgs& a, float4* handoff,
                     const size_t rec = ((size_t)b * gridDim.y + g) * H * W + (size_t)i * W + j;
                     __stcg(a.hs + (rec * 4 + c) * 32 + lane, hv);
                 }
+            }
+
+            if (STORE_HS) {
+                // d_C[pixel][n] = sum over channels of gy*h: finish over the 8 cq lanes, then one
+                // atomic per state from the even-cq lane of each pair
+                const bool hi16 = (cq & 4) != 0, hi8 = (cq & 2) != 0;
+                float k0 = hi16 ? dC[2] : dC[0], k1 = hi16 ? dC[3] : dC[1];
+                k0 += __shfl_xor_sync(0xffffffffu, hi16 ? dC[0] : dC[2], 16);
+                k1 += __shfl_xor_sync(0xffffffffu, hi16 ? dC[1] : dC[3], 16);
+                float k = hi8 ? k1 : k0;
+                k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
+                k += __shfl_xor_sync(0xffffffffu, k, 4);
+                const int nn = n0 + (hi16 ? 2 : 0) + (hi8 ? 1 : 0);
+                if ((cq & 1) == 0 && nn < a.N) atomicAdd(a.accBC + pix * 48 + 32 + nn, k);
             }
 
             if (a.y != nullptr) {

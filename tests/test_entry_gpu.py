@@ -1,0 +1,74 @@
+"""The op as the backbone calls it: wavefront_scan_cuda(x, weights..., recomp) with autograd,
+against fixtures produced by the reference project's own Python + kernel code run on the CPU."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import inputs
+from helpers import GOLDEN, rel_err, sub
+
+pytestmark = pytest.mark.gpu
+
+WNAMES = ("AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w", "dt_projL_b", "D")
+
+
+def _load(name):
+    g = np.load(os.path.join(GOLDEN, f"{name}.npz"))
+    B, H, W, E, N = (int(v) for v in g["shape"])
+    seed = int(g["seed"])
+    w = inputs.make_module_params(E, N, seed=seed)
+    gen = torch.Generator().manual_seed(seed + 100)
+    x = torch.randn(B, H, W, E, generator=gen)
+    gy = torch.randn(B, H, W, E, generator=gen)
+    return g, w, x, gy
+
+
+@pytest.mark.parametrize("name,dt,tol", [("entry_f32", torch.float32, 1e-4), ("entry_bf16", torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("recomp", ["partial", "full"])
+def test_entry_matches_reference_fixture(name, dt, tol, recomp):
+    from mamba2d_b200 import wavefront_scan_cuda
+    g, w, x0, gy = _load(name)
+    x = x0.to("cuda", dt).requires_grad_(True)
+    ws = [w[k].clone().cuda().requires_grad_(True) for k in WNAMES]
+    y = wavefront_scan_cuda(x, *ws, recomp)
+    assert y.dtype == dt and y.shape == x.shape and y.is_contiguous()
+    grads = torch.autograd.grad(y, [x] + ws, gy.to("cuda", dt))
+    assert rel_err(sub(y), g[f"{recomp}_y"]) < tol
+    assert rel_err(sub(grads[0]), g[f"{recomp}_d_x"]) < tol
+    # weight gradients pass through bf16 GEMMs on both sides; allow the bf16 bar for those
+    for k, gr in zip(WNAMES, grads[1:]):
+        assert gr.dtype == torch.float32
+        assert rel_err(sub(gr), g[f"{recomp}_d_{k}"]) < (tol if dt == torch.float32 else 4e-2), k
+
+
+def test_entry_errors_match_reference():
+    from mamba2d_b200 import wavefront_scan_cuda
+    w = inputs.make_module_params(32, 16, seed=1)
+    ws = [w[k].cuda() for k in WNAMES]
+    with pytest.raises(ValueError):
+        wavefront_scan_cuda(torch.randn(1, 1, 8, 32, device="cuda"), *ws)
+    with pytest.raises(ValueError):
+        wavefront_scan_cuda(torch.randn(1, 8, 1, 32, device="cuda"), *ws)
+    with pytest.raises(ValueError):
+        wavefront_scan_cuda(torch.randn(1, 4, 4, 32, device="cuda"), *ws, "sometimes")
+
+
+def test_entry_autocast_and_inference_mode():
+    from mamba2d_b200 import wavefront_scan_cuda
+    w = inputs.make_module_params(64, 16, seed=2)
+    ws = [w[k].cuda() for k in WNAMES]
+    x = torch.randn(2, 8, 8, 64, device="cuda")
+    with torch.inference_mode():
+        y32 = wavefront_scan_cuda(x, *ws)
+        y16 = wavefront_scan_cuda(x.bfloat16(), *ws)
+    assert y16.dtype == torch.bfloat16
+    assert rel_err(y16.float().cpu().numpy(), y32.cpu().numpy()) < 3e-2
+
+
+def test_no_cpu_fallback():
+    from mamba2d_b200 import scan_fwd
+    inp = inputs.make_inputs(1, 4, 4, 32, 16, seed=1)
+    with pytest.raises(RuntimeError):
+        scan_fwd(*[inp[k] for k in ("x", "dT", "dL", "AT", "AL", "BT", "BL", "C", "D")])

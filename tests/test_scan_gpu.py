@@ -92,3 +92,49 @@ def test_forward_matches_reference_fixture(name):
     inp, g = load_scan_golden(name)
     y = run_fwd(inp, kind)
     assert rel_err(sub(y), g["y"]) < TOL[kind]
+
+
+BWD_SHAPES = [
+    (2, 32, 32, 64, 16),
+    (2, 5, 4, 6, 4),
+    (1, 2, 2, 32, 16),
+    (3, 7, 7, 64, 16),
+    (2, 14, 14, 96, 16),
+    (1, 28, 28, 128, 16),
+    (1, 56, 56, 64, 16),
+    (1, 9, 13, 40, 12),
+    (1, 13, 3, 32, 16),
+    (5, 3, 19, 32, 8),
+]
+
+
+@pytest.mark.parametrize("shape", BWD_SHAPES)
+@pytest.mark.parametrize("kind", ["f32", "bf16"])
+@pytest.mark.parametrize("strided", [False, True])
+def test_backward_matches_oracle(shape, kind, strided):
+    inp = inputs.make_inputs(*shape, seed=sum(shape) + 1, strided_bc=strided)
+    ref_in = bf16_round_inputs(inp) if kind == "bf16" else inp
+    ref = cpu.backward(ref_in, mode="f64")
+    got = run_bwd(inp, kind)
+    for k in GRADS:
+        assert rel_err(got[k], ref[k]) < TOL[kind], k
+
+
+@pytest.mark.parametrize("name", sorted(SCAN_GOLDEN))
+def test_backward_matches_reference_fixture(name):
+    strided, kind = SCAN_GOLDEN[name]
+    if kind == "f64":
+        pytest.skip("fp64 is not a dtype of the CUDA path")
+    inp, g = load_scan_golden(name)
+    got = run_bwd(inp, kind)
+    for k in GRADS:
+        assert rel_err(sub(got[k]), g[k]) < TOL[kind], k
+
+
+def test_backward_twice_same_workspace_sizes():
+    """Accumulators are re-zeroed on every call: two calls give the same answer."""
+    inp = inputs.make_inputs(2, 14, 14, 64, 16, seed=9)
+    a = run_bwd(inp, "f32")
+    b = run_bwd(inp, "f32")
+    for k in GRADS:
+        assert rel_err(a[k], b[k]) < 1e-5, k
