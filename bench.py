@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""Benchmark of the wavefront 2-D selective scan (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype f32|bf16] [--impl ours|reference]
+
+Workload ("config 2" of the baseline description): the isolated scan at the four M2D-T stage
+shapes, batch 128 per GPU, N = 16 states:  (D, H=W) = (64,56) (128,28) (320,14) (512,7).
+One step = forward + backward of all four shapes on one batch of seeded synthetic inputs.
+An element is one output scalar y[b,i,j,e]; elements per step = sum of B*H*W*D = 49 774 592.
+
+Prints ONE JSON line on rank 0.  `value` is device-resident throughput (CUDA events around the
+timed steps, max over ranks); `e2e` is the same work driven from pinned host buffers with the
+host<->device copies inside the timed region; `roofline` is for the dominant kernel (the backward
+kernel at the 56x56 shape), `roofline_step` for everything launched in a step; `cpu_baseline` is
+the C/OpenMP restatement under oracle/ timed on this machine's host cores on a bounded sample.
+
+`--impl reference` times that CPU restatement as the reference arm: the reference project has no
+CPU implementation of this path (its launcher has no host branch), so the restatement of its
+kernel body is what can run on host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+STAGES = [(64, 56), (128, 28), (320, 14), (512, 7)]   # (D, H=W)
+BATCH = 128
+NSTATE = 16
+ORDER = ("x", "dT", "dL", "AT", "AL", "BT", "BL", "C", "D")
+METRIC = "2D-scan fwd+bwd elements/s"
+UNIT = "elements/s"
+BYTES = {"f32": 4, "bf16": 2}
+
+# DRAM bytes (read + write) of ONE launch of the dominant kernel, from an ncu capture of this same
+# workload; see profiles/ for the capture summaries.  None = not captured for that dtype.
+NCU_TRAFFIC = {"f32": None, "bf16": None}
+
+
+def fwd_bytes(D, HW, s, B=BATCH, N=NSTATE):
+    return s * (4 + 3 * N / D) * B * HW * HW * D
+
+
+def bwd_bytes(D, HW, s, B=BATCH, N=NSTATE):
+    return s * (7 + 6 * N / D) * B * HW * HW * D
+
+
+def elements(B=BATCH):
+    return sum(B * hw * hw * d for d, hw in STAGES)
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while running."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        busy = [v for v in sm if mx and v > 0.5 * mx] or sm
+        return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_stage_inputs(dtype, device, pinned_host=False):
+    """Seeded synthetic inputs for every stage shape (seed 0, draws as oracle.inputs documents)."""
+    import torch
+    from oracle import inputs as oin           # input generator only (no oracle compute)
+    tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+    out = []
+    for D, HW in STAGES:
+        inp = oin.make_inputs(BATCH, HW, HW, D, NSTATE, seed=0, strided_bc=True)
+        host = {}
+        for k, v in inp.items():
+            base = v if v.is_contiguous() else v._base
+            hb = base.to(tdt)
+            if pinned_host:
+                hb = hb.pin_memory()
+            host[k] = (hb, v.shape, v.stride(), v.storage_offset(), v.is_contiguous())
+        out.append(host)
+    return out
+
+
+def to_device(host, device):
+    d, seen = {}, {}
+    for k, (hb, shape, stride, off, contig) in host.items():
+        key = hb.data_ptr()
+        if key not in seen:
+            seen[key] = hb.to(device, non_blocking=True)
+        d[k] = seen[key] if contig else seen[key].as_strided(shape, stride, off)
+    return d
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from mamba2d_b200 import scan_bwd, scan_fwd
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path for the product)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    host = make_stage_inputs(args.dtype, dev, pinned_host=True)
+    devin = [to_device(h, dev) for h in host]
+    torch.cuda.synchronize()
+    s = BYTES[args.dtype]
+
+    def step(record=None):
+        for si, d in enumerate(devin):
+            a = [d[k] for k in ORDER]
+            if record is not None:
+                record[si][0].record()
+            scan_fwd(*a)
+            if record is not None:
+                record[si][1].record()
+            scan_bwd(*a, d["gy"])
+            if record is not None:
+                record[si][2].record()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev = [[[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in STAGES] for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for k in range(args.steps):
+        step(ev[k])
+    t1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms_total = t0.elapsed_time(t1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+
+    # per-kernel durations (averages over the timed steps, this rank)
+    per = []
+    for si, (D, HW) in enumerate(STAGES):
+        f = sum(ev[k][si][0].elapsed_time(ev[k][si][1]) for k in range(args.steps)) / args.steps
+        b = sum(ev[k][si][1].elapsed_time(ev[k][si][2]) for k in range(args.steps)) / args.steps
+        per.append({"D": D, "HW": HW, "fwd_ms": round(f, 4), "bwd_ms": round(b, 4),
+                    "fwd_GBs": round(fwd_bytes(D, HW, s) / f / 1e6, 1), "bwd_GBs": round(bwd_bytes(D, HW, s) / b / 1e6, 1),
+                    "fb_GBs": round((fwd_bytes(D, HW, s) + bwd_bytes(D, HW, s)) / (f + b) / 1e6, 1)})
+
+    # ---- end to end from pinned host buffers: H2D of the step's inputs, D2H of y and the gradients
+    e2e_steps = max(2, min(args.steps, 3))
+    outs_host = None
+    h2d = d2h = 0
+
+    def e2e_step():
+        nonlocal outs_host, h2d, d2h
+        h2d = d2h = 0
+        first = outs_host is None
+        if first:
+            outs_host = []
+        for si, h in enumerate(host):
+            d = to_device(h, dev)
+            seen = set()
+            for hb, *_ in h.values():
+                if hb.data_ptr() not in seen:
+                    seen.add(hb.data_ptr())
+                    h2d += hb.numel() * hb.element_size()
+            a = [d[k] for k in ORDER]
+            y = scan_fwd(*a)
+            grads = scan_bwd(*a, d["gy"])
+            res = (y, *grads)
+            if first:
+                outs_host.append([torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in res])
+            for hb, t in zip(outs_host[si], res):
+                hb.copy_(t, non_blocking=True)
+                d2h += t.numel() * t.element_size()
+
+    e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    c0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - c0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    clocks = sampler.stop() if sampler else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_peak()
+    el = elements()
+    dom = per[0]
+    dom_bytes = bwd_bytes(*STAGES[0], s)
+    step_bytes = sum(fwd_bytes(D, HW, s) + bwd_bytes(D, HW, s) for D, HW in STAGES)
+    step_kernel_ms = sum(p["fwd_ms"] + p["bwd_ms"] for p in per)
+    out = {
+        "metric": METRIC, "value": el * world / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+        "config": {"workload": "isolated scan fwd+bwd at the four M2D-T stage shapes "
+                               "(D,H=W)=(64,56),(128,28),(320,14),(512,7), batch 128 per GPU, N=16, BT/BL/C as "
+                               "strided views (pitch 2R+3N)",
+                   "elements_per_step_per_gpu": el, "l2": "each step streams >3 GB (inputs + state record), "
+                   "far larger than the 126 MB L2, so no flush is needed between iterations",
+                   "parallelism": f"batch-sharded replicas x{world}, no data-path collective"},
+        "e2e": {"value": el * world * e2e_steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "note": "pinned host inputs -> device, fwd+bwd through the public API, y and all nine gradients -> pinned host"},
+        "gpu_launches": args.steps * len(STAGES) * 3,
+        "roofline": {"bound": "hbm", "kernel": "m2d_bwd_kernel @ D=64,H=W=56,B=128", "achieved": dom_bytes / dom["bwd_ms"] / 1e6,
+                     "peak": peak, "unit": "GB/s", "frac": dom_bytes / dom["bwd_ms"] / 1e6 / peak,
+                     "peak_kind": peak_kind, "algorithmic_bytes": dom_bytes, "ms": dom["bwd_ms"],
+                     "traffic": NCU_TRAFFIC[args.dtype]},
+        "roofline_step": {"bound": "hbm", "achieved": step_bytes / step_kernel_ms / 1e6, "peak": peak, "unit": "GB/s",
+                          "frac": step_bytes / step_kernel_ms / 1e6 / peak, "algorithmic_bytes": step_bytes},
+        "per_shape": per,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_baseline(args.dtype)
+    print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(dtype, sample_batch=16, repeat=1, threads=None):
+    """The C/OpenMP restatement (oracle/) timed on the host cores over a bounded sample: forward +
+    backward of the four stage shapes at a reduced batch."""
+    import torch
+    from oracle import cpu as ocpu
+    from oracle import inputs as oin
+    if threads:
+        ocpu.set_threads(threads)
+    cores = ocpu.num_threads()
+    el = 0
+    t = 0.0
+    for D, HW in STAGES:
+        inp = oin.make_inputs(sample_batch, HW, HW, D, NSTATE, seed=0)
+        if dtype == "bf16":
+            inp = {k: v.to(torch.bfloat16).float() for k, v in inp.items()}
+        for _ in range(repeat):
+            c0 = time.perf_counter()
+            ocpu.forward(inp, "f32")
+            ocpu.backward(inp, mode="f32")
+            t += time.perf_counter() - c0
+            el += sample_batch * HW * HW * D
+    return {"value": el / t, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"fwd+bwd of the four stage shapes at batch {sample_batch} (of 128), fp32 arithmetic, "
+                      f"{repeat} pass(es), {t:.1f} s wall on {cores} threads",
+            "seconds": t}
+
+
+def run_reference(args):
+    """Reference arm: the reference's algorithm on host cores (see module docstring)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    sample_batch = 8
+    times, el = [], 0
+    for k in range(args.warmup + args.steps):
+        r = cpu_baseline(args.dtype, sample_batch=sample_batch)
+        if k >= args.warmup:
+            times.append(r["seconds"])
+            el = r["value"] * r["seconds"]
+    ms = 1e3 * sum(times) / len(times)
+    value = el / (ms * 1e-3)
+    out = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": args.dtype, "data": "synthetic",
+           "config": {"workload": "isolated scan fwd+bwd at the four M2D-T stage shapes, N=16; each step is a bounded "
+                                  f"sample at batch {sample_batch} of 128 on the host cores"},
+           "cpu_baseline": {"value": value, "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+           "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "gpu_launches": 0}
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--dtype", choices=("f32", "bf16"), default="f32")
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

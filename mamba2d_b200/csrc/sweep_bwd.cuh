@@ -32,10 +32,14 @@ struct RevIn {
 template <typename io_t, bool VEC>
 __device__ __forceinline__ void load_rev(RevIn& ri, const ScanArgs& a, int b, int g, int i, int j, int lane, int ch0, int chv, int n0, int nv) {
     const long long pix = ((long long)b * a.H + i) * a.W + j;
-    ri.gy = load4<VEC>(static_cast<const io_t*>(a.gy), pix * a.E + ch0, chv);
-    ri.x = load4<VEC>(static_cast<const io_t*>(a.x), pix * a.E + ch0, chv);
-    ri.dT = load4<VEC>(static_cast<const io_t*>(a.dT), pix * a.E + ch0, chv);
-    ri.dL = load4<VEC>(static_cast<const io_t*>(a.dL), pix * a.E + ch0, chv);
+    if (chv > 0) {   // see load_cell: never read beyond the last channel
+        ri.gy = load4<VEC>(static_cast<const io_t*>(a.gy), pix * a.E + ch0, chv);
+        ri.x = load4<VEC>(static_cast<const io_t*>(a.x), pix * a.E + ch0, chv);
+        ri.dT = load4<VEC>(static_cast<const io_t*>(a.dT), pix * a.E + ch0, chv);
+        ri.dL = load4<VEC>(static_cast<const io_t*>(a.dL), pix * a.E + ch0, chv);
+    } else {
+        ri.gy = ri.x = ri.dT = ri.dL = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     if (nv > 0) {
         ri.bT = load4<VEC>(static_cast<const io_t*>(a.BT), pix * a.pBT + n0, nv);
         ri.bL = load4<VEC>(static_cast<const io_t*>(a.BL), pix * a.pBL + n0, nv);

@@ -45,10 +45,16 @@ struct CellIn {
 
 template <typename io_t, bool VEC, bool WITH_GY>
 __device__ __forceinline__ void load_cell(CellIn& ci, const FwdArgs& a, long long pix, int ch0, int chv, int n0, int nv) {
-    if (WITH_GY) ci.gy = load4<VEC>(static_cast<const io_t*>(a.gy), pix * a.E + ch0, chv);
-    ci.x = load4<VEC>(static_cast<const io_t*>(a.x), pix * a.E + ch0, chv);
-    ci.dT = load4<VEC>(static_cast<const io_t*>(a.dT), pix * a.E + ch0, chv);
-    ci.dL = load4<VEC>(static_cast<const io_t*>(a.dL), pix * a.E + ch0, chv);
+    // lanes whose channel block lies beyond E (last group of a width that is not a multiple of 32)
+    // must not touch memory: a vector load there would read the next pixel
+    if (chv > 0) {
+        if (WITH_GY) ci.gy = load4<VEC>(static_cast<const io_t*>(a.gy), pix * a.E + ch0, chv);
+        ci.x = load4<VEC>(static_cast<const io_t*>(a.x), pix * a.E + ch0, chv);
+        ci.dT = load4<VEC>(static_cast<const io_t*>(a.dT), pix * a.E + ch0, chv);
+        ci.dL = load4<VEC>(static_cast<const io_t*>(a.dL), pix * a.E + ch0, chv);
+    } else {
+        ci.gy = ci.x = ci.dT = ci.dL = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     if (nv > 0) {
         ci.bT = load4<VEC>(static_cast<const io_t*>(a.BT), pix * a.pBT + n0, nv);
         ci.bL = load4<VEC>(static_cast<const io_t*>(a.BL), pix * a.pBL + n0, nv);

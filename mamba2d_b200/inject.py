@@ -1,0 +1,91 @@
+"""Make the reference project's unchanged model code call this package's scan.
+
+The reference's ``models/mamba2d.py`` does ``from .kernels.wavefront_cuda import wavefront_scan_cuda``
+(models/mamba2d.py:10) and its downstream copy does the same relative import
+(downstream/Mamba2D/mamba2d.py:13).  Importing that module normally JIT-builds the reference's CUDA
+extension.  ``install()`` pre-registers this package's ``wavefront_cuda`` under the module names
+those imports resolve to, so the reference files load unmodified and ``M2DBlock.ssm`` reaches the
+B200 kernels.
+
+    import mamba2d_b200.inject as inject
+    inject.install("/path/to/Mamba2D")          # adds the checkout to sys.path
+    from models.mamba2d import Mamba2DBackbone
+"""
+import importlib
+import sys
+import types
+
+from . import wavefront_cuda
+
+TARGETS = ("models.kernels.wavefront_cuda", "Mamba2D.kernels.wavefront_cuda", "kernels.wavefront_cuda")
+
+
+def _ensure_package(name, path=None):
+    if name in sys.modules:
+        return sys.modules[name]
+    mod = types.ModuleType(name)
+    mod.__path__ = [path] if path else []
+    sys.modules[name] = mod
+    return mod
+
+
+def install(reference_root=None, extra_targets=()):
+    """Register the replacement under every module path the reference imports it by.
+
+    ``reference_root`` (optional) is put on ``sys.path`` so ``import models.mamba2d`` finds the
+    reference checkout.  Returns the list of module names that now resolve to this package."""
+    import os
+    if reference_root and reference_root not in sys.path:
+        sys.path.insert(0, reference_root)
+    done = []
+    for target in tuple(TARGETS) + tuple(extra_targets):
+        parts = target.split(".")
+        # the ``kernels`` sub-package must exist as a package object for the relative import
+        if reference_root:
+            kdir = os.path.join(reference_root, *parts[:-1]) if parts[0] != "Mamba2D" else \
+                os.path.join(reference_root, "downstream", *parts[:-1])
+        else:
+            kdir = None
+        if len(parts) > 2:
+            try:
+                importlib.import_module(parts[0])
+            except Exception:
+                _ensure_package(parts[0])
+        _ensure_package(".".join(parts[:-1]), kdir)
+        sys.modules[target] = wavefront_cuda
+        done.append(target)
+    return done
+
+
+def install_droppath_shim():
+    """``models/mamba2d.py`` imports ``timm.layers.DropPath``.  Where timm is not installed, provide
+    a minimal stand-in (stochastic depth; identity in eval mode) so the backbone can be built."""
+    try:
+        import timm.layers  # noqa: F401
+        return False
+    except Exception:
+        pass
+    import torch
+    import torch.nn as nn
+
+    class DropPath(nn.Module):
+        def __init__(self, drop_prob: float = 0.0, scale_by_keep: bool = True):
+            super().__init__()
+            self.drop_prob, self.scale_by_keep = drop_prob, scale_by_keep
+
+        def forward(self, x):
+            if self.drop_prob == 0.0 or not self.training:
+                return x
+            keep = 1 - self.drop_prob
+            mask = x.new_empty((x.shape[0],) + (1,) * (x.ndim - 1)).bernoulli_(keep)
+            if keep > 0.0 and self.scale_by_keep:
+                mask.div_(keep)
+            return x * mask
+
+    timm = types.ModuleType("timm")
+    layers = types.ModuleType("timm.layers")
+    layers.DropPath = DropPath
+    timm.layers = layers
+    sys.modules.setdefault("timm", timm)
+    sys.modules.setdefault("timm.layers", layers)
+    return True

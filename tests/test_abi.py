@@ -1,0 +1,83 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/m2d_scan.h declares;
+argument validation and launch planning run on the host."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from mamba2d_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    from mamba2d_b200 import build
+    build.build()
+    return _lib.lib()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "m2d_scan.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(m2d_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(L):
+    syms = declared_symbols()
+    assert set(_lib.EXPORTS) <= set(syms)
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for s in syms:
+        assert getattr(raw, s) is not None, s
+
+
+def test_version_and_strerror(L):
+    assert L.m2d_abi_version() == _lib.ABI_VERSION
+    assert _lib.strerror(0) == "ok"
+    for code in range(-9, 0):
+        assert _lib.strerror(code) not in ("ok", "unknown status")
+    assert _lib.strerror(-99) == "unknown status"
+
+
+def _desc(**kw):
+    d = _lib.ScanDesc()
+    d.struct_bytes = ctypes.sizeof(_lib.ScanDesc)
+    d.dtype = _lib.M2D_F32
+    d.B, d.H, d.W, d.E, d.N = 2, 8, 8, 64, 16
+    d.BT_pitch = d.BL_pitch = d.C_pitch = 16
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+def test_descriptor_validation_without_a_device(L):
+    d = _desc()
+    assert L.m2d_scan_fwd(ctypes.byref(d), None) == -1          # NULL pointers
+    assert L.m2d_scan_fwd(ctypes.byref(_desc(H=1)), None) == -3  # H < 2, as the reference's ValueError
+    assert L.m2d_scan_fwd(ctypes.byref(_desc(W=1)), None) == -3
+    assert L.m2d_scan_bwd(ctypes.byref(_desc(N=32)), None) == -4
+    assert L.m2d_scan_fwd(ctypes.byref(_desc(dtype=7)), None) == -2
+    assert L.m2d_scan_fwd(ctypes.byref(_desc(C_pitch=8)), None) == -5
+    assert L.m2d_scan_fwd(ctypes.byref(_desc(struct_bytes=8)), None) == -8
+    assert L.m2d_scan_fwd(None, None) == -1
+
+
+def test_workspace_queries(L):
+    # one band (H <= 8 row-warps): the forward needs no scratch
+    assert L.m2d_scan_fwd_workspace(ctypes.byref(_desc())) == 0
+    # several bands: a per-CTA ring of W slots of 2 KiB
+    d = _desc(B=128, H=56, W=56)
+    ws = L.m2d_scan_fwd_workspace(ctypes.byref(d))
+    assert ws > 0 and ws % 256 == 0 and ws <= 128 * 2 * 56 * 2048
+    # backward: state record B*groups*H*W*2 KiB plus accumulators
+    wb = L.m2d_scan_bwd_workspace(ctypes.byref(d))
+    assert wb >= 128 * 2 * 56 * 56 * 2048
+    assert L.m2d_scan_fwd_workspace(ctypes.byref(_desc(H=1))) == 0    # invalid descriptor
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_LIB", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.lib()

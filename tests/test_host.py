@@ -1,0 +1,74 @@
+"""Host-side logic of the Python boundary that needs no GPU."""
+import inspect
+
+import pytest
+import torch
+
+from mamba2d_b200 import wavefront_cuda as wc
+from oracle import inputs, torch_ref
+
+
+def test_public_signature_matches_reference_entry():
+    """Argument names and order of the reference's wavefront_scan_cuda
+    (models/kernels/wavefront_cuda.py:315 in the reference)."""
+    params = list(inspect.signature(wc.wavefront_scan_cuda).parameters)
+    assert params == ["x", "AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w",
+                      "dt_projL_b", "D", "recomp"]
+    assert inspect.signature(wc.wavefront_scan_cuda).parameters["recomp"].default == "partial"
+    assert list(inspect.signature(wc.wf_cuda_fn_pr.forward).parameters)[1:] == \
+        ["x", "deltaT", "deltaL", "AT", "AL", "BT", "BL", "C", "D"]
+    assert list(inspect.signature(wc.proj_params).parameters) == \
+        ["x", "AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w", "dt_projL_b"]
+
+
+def test_value_errors_raised_before_any_device_work():
+    w = inputs.make_module_params(32, 16, seed=1)
+    ws = [w[k] for k in ("AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w", "dt_projL_b", "D")]
+    with pytest.raises(ValueError, match="spatial dims"):
+        wc.wavefront_scan_cuda(torch.randn(1, 1, 4, 32), *ws)
+    with pytest.raises(ValueError, match="Unknown recomputation mode"):
+        wc.wavefront_scan_cuda(torch.randn(1, 4, 4, 32), *ws, recomp="none")
+
+
+def test_cpu_tensors_are_rejected_not_silently_computed():
+    inp = inputs.make_inputs(1, 4, 4, 32, 16, seed=1)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        wc.scan_fwd(*[inp[k] for k in ("x", "dT", "dL", "AT", "AL", "BT", "BL", "C", "D")])
+
+
+def test_shape_and_dtype_checks():
+    inp = inputs.make_inputs(1, 4, 4, 32, 16, seed=1)
+    a = {k: v.to("meta") for k, v in inp.items()}
+    order = ("x", "dT", "dL", "AT", "AL", "BT", "BL", "C", "D")
+    with pytest.raises(RuntimeError):
+        wc._check_inputs(*[a[k] for k in order])               # not CUDA
+
+    class FakeCuda(torch.Tensor):
+        pass
+    # shape check happens on metadata only
+    bad = dict(inp)
+    bad["dT"] = inp["dT"][:, :3]
+    with pytest.raises(RuntimeError):
+        wc._check_inputs(*[bad[k] for k in order])
+
+
+def test_pixel_pitch_detection():
+    inp = inputs.make_inputs(2, 5, 6, 64, 16, seed=2, strided_bc=True)
+    t, pitch = wc._pixel_pitch(inp["BT"], 5, 6, 16)
+    assert pitch == 2 * 4 + 3 * 16 and t.data_ptr() == inp["BT"].data_ptr()
+    t, pitch = wc._pixel_pitch(inp["BT"].contiguous(), 5, 6, 16)
+    assert pitch == 16
+    weird = inp["BT"].permute(0, 2, 1, 3)                      # not a pixel-pitched view
+    t, pitch = wc._pixel_pitch(weird, 6, 5, 16)
+    assert pitch == 16 and t.is_contiguous()
+
+
+def test_proj_params_equals_restatement_on_cpu():
+    w = inputs.make_module_params(32, 16, seed=3)
+    x = torch.randn(2, 4, 5, 32)
+    names = ("AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w", "dt_projL_b")
+    a = wc.proj_params(x, *[w[k] for k in names])
+    b = torch_ref.proj_params_ref(x, *[w[k] for k in names])
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)
+    assert not a[4].is_contiguous()     # BT stays a view into the projection output
