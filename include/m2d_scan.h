@@ -111,6 +111,29 @@ int m2d_scan_fwd(const m2d_scan_desc *desc, void *stream);
  */
 int m2d_scan_bwd(const m2d_scan_desc *desc, void *stream);
 
+/*
+ * Forward scan that needs no workspace from the caller.  It has no counterpart in the reference
+ * project (there, Python allocates every buffer the kernels touch).
+ *
+ * Same inputs, output and results as m2d_scan_fwd, but desc->workspace is ignored: the scratch the
+ * kernel needs lives in a fixed array inside the library.  It exists for callers that cannot
+ * provide a scratch buffer -- a host runtime whose plugin signature carries only inputs and
+ * outputs, a process that handed out all device memory at start-up, or a loop that must never
+ * reach cudaMalloc.  The entry point itself calls no cudaMalloc/cudaFree and no allocating
+ * library routine.
+ *
+ *   - The array is M2D_NOALLOC_SCRATCH_BYTES (32 MiB) and every GPU that loads the library keeps
+ *     it until the process exits.
+ *   - A problem needing more scratch than that returns M2D_ERR_TOO_LARGE before any device work
+ *     (the need is what m2d_scan_fwd_workspace() reports).
+ *   - All calls on a device share the array.  Nothing in it must be zero on entry, but calls that
+ *     overlap in time on one GPU race on it: keep them on one stream or order them with events.
+ *   - The first call on each device resolves the array's device address and caches it; issue
+ *     that first call before any stream capture on that device.
+ */
+#define M2D_NOALLOC_SCRATCH_BYTES (32u << 20)
+int m2d_scan_fwd_noalloc(const m2d_scan_desc *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

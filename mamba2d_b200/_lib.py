@@ -11,9 +11,10 @@ LIB_PATH = os.path.join(HERE, "libm2d_scan.so")
 
 M2D_F32, M2D_BF16 = 0, 1
 ABI_VERSION = 1
+NOALLOC_SCRATCH_BYTES = 32 << 20     # M2D_NOALLOC_SCRATCH_BYTES in include/m2d_scan.h
 
 EXPORTS = ("m2d_abi_version", "m2d_strerror", "m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace",
-           "m2d_scan_fwd", "m2d_scan_bwd")
+           "m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc")
 
 
 class ScanDesc(ctypes.Structure):
@@ -52,7 +53,7 @@ def lib():
         for name in ("m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace"):
             getattr(L, name).restype = ctypes.c_uint64
             getattr(L, name).argtypes = [ctypes.POINTER(ScanDesc)]
-        for name in ("m2d_scan_fwd", "m2d_scan_bwd"):
+        for name in ("m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc"):
             getattr(L, name).restype = ctypes.c_int
             getattr(L, name).argtypes = [ctypes.POINTER(ScanDesc), ctypes.c_void_p]
         if L.m2d_abi_version() != ABI_VERSION:

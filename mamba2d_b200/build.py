@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OUT = os.path.join(HERE, "libm2d_scan.so")
-SOURCES = ["m2d_abi.cu", "m2d_scan_fwd.cu", "m2d_scan_bwd.cu"]
+SOURCES = ["m2d_abi.cu", "m2d_scan_fwd.cu", "m2d_scan_bwd.cu", "m2d_scan_fwd_noalloc.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

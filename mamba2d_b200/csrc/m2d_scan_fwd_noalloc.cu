@@ -1,0 +1,108 @@
+// Forward scan for callers that cannot hand the library a workspace buffer.
+//
+// The regular forward entry point needs a scratch region (the per-CTA ring that carries the last
+// row of one band of image rows to the first row of the next band) and expects the caller to
+// allocate it.  Some callers have no way to do that: a host runtime that binds this library behind
+// a fixed "inputs in, outputs out" plugin signature has no slot for an extra buffer; a service that
+// carved up all device memory at start-up has no allocator left to ask; and code running inside a
+// latency-critical loop must not call cudaMalloc, which can synchronise the whole device.  For
+// them this file keeps the ring in a file-scope __device__ array of fixed size, so the call needs
+// nothing but the inputs and the output.
+//
+// Cost and limits of that choice:
+//   - every GPU on which this library is loaded holds M2D_NOALLOC_SCRATCH_BYTES (32 MiB) of
+//     device memory from load until the process exits;
+//   - problems whose ring would not fit are rejected with M2D_ERR_TOO_LARGE;
+//   - all calls on one device share the one array.  Nothing in it has to start at zero (every slot
+//     is written before it is read within a call, and what an earlier call left behind is never
+//     read), but two calls that overlap in time on the same GPU -- different streams, or different
+//     host threads -- would overwrite each other's slots and produce wrong results.  Serialise
+//     them (one stream, or events between streams);
+//   - the first call on each device looks up the array's device address
+//     (cudaGetSymbolAddress) and caches it; make that first call before starting any stream
+//     capture on that device.
+#include <mutex>
+
+#include "plan.cuh"
+#include "sweep_fwd.cuh"
+
+namespace m2d {
+
+// In host code this name is only a handle for the runtime's symbol table, not a device address:
+// it must go through cudaGetSymbolAddress before a kernel can be given a pointer to it.
+static __device__ __align__(256) unsigned char g_noalloc_ring[M2D_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_ring_mutex;
+static float4* g_ring_ptr[kMaxDevices] = {};   // device address of g_noalloc_ring on each device
+
+// Device address of the ring on the CURRENT device; looked up once per device.
+static int ring_address(float4** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return M2D_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(g_ring_mutex);
+    if (g_ring_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_ring) != cudaSuccess || p == nullptr) {
+            cudaGetLastError();
+            return M2D_ERR_LAUNCH;
+        }
+        g_ring_ptr[dev] = static_cast<float4*>(p);
+    }
+    *out = g_ring_ptr[dev];
+    return M2D_OK;
+}
+
+template <typename io_t, bool VEC>
+__global__ void __launch_bounds__(256, 2) m2d_fwd_noalloc_kernel(const ScanArgs a) {
+    extern __shared__ float4 handoff[];
+    const int lane = threadIdx.x & 31;
+    const int cq = lane >> 2, nq = lane & 3;
+    const int g = blockIdx.y;
+    const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
+    const int chv = min(4, max(0, a.E - ch0));
+    const int nv = min(4, max(0, a.N - n0));
+    const int total = 2 * ((blockDim.x >> 5) + 1) * kSlotF4;
+    for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float aT2[4][4], aL2[4][4];
+    load_param_block<io_t>(aT2, a.AT, a.N, ch0, chv, n0, nv, kLog2e);
+    load_param_block<io_t>(aL2, a.AL, a.N, ch0, chv, n0, nv, kLog2e);
+    const int ch_own = g * kGroup + lane;
+    const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
+    __syncthreads();
+    const int nb = (a.B - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    forward_sweep<io_t, VEC, false>(a, handoff, aT2, aL2, D_own, blockIdx.x, gridDim.x, nb);
+}
+
+template <typename io_t>
+static int launch_noalloc(const m2d_scan_desc* d, const Plan& pl, bool vec, float4* ring, cudaStream_t st) {
+    ScanArgs a = {};
+    a.B = d->B; a.H = d->H; a.W = d->W; a.E = d->E; a.N = d->N;
+    a.x = d->x; a.dT = d->dT; a.dL = d->dL; a.AT = d->AT; a.AL = d->AL;
+    a.BT = d->BT; a.BL = d->BL; a.C = d->C; a.D = d->D;
+    a.pBT = d->BT_pitch; a.pBL = d->BL_pitch; a.pC = d->C_pitch;
+    a.y = d->y;
+    a.ring = ring;
+    a.Rb = pl.Rb; a.nbands = pl.nbands;
+    dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
+    if (vec) m2d_fwd_noalloc_kernel<io_t, true><<<grid, block, pl.smem, st>>>(a);
+    else m2d_fwd_noalloc_kernel<io_t, false><<<grid, block, pl.smem, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
+}
+
+}  // namespace m2d
+
+extern "C" int m2d_scan_fwd_noalloc(const m2d_scan_desc* d, void* stream) {
+    int rc = m2d::check_desc(d, false, true);
+    if (rc != M2D_OK) return rc;
+    if (!d->y) return M2D_ERR_NULL;
+    const m2d::Plan pl = m2d::plan_fwd(d);
+    if (pl.scratch > M2D_NOALLOC_SCRATCH_BYTES) return M2D_ERR_TOO_LARGE;   // decided before any device work
+    float4* ring = nullptr;
+    rc = m2d::ring_address(&ring);
+    if (rc != M2D_OK) return rc;
+    const bool vec = m2d::vector_ok(d, false);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (d->dtype == M2D_F32) return m2d::launch_noalloc<float>(d, pl, vec, ring, st);
+    return m2d::launch_noalloc<__nv_bfloat16>(d, pl, vec, ring, st);
+}
