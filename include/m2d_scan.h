@@ -49,7 +49,8 @@ typedef enum m2d_status {
     M2D_ERR_WORKSPACE = -6,     /* workspace missing, too small or not 256-byte aligned */
     M2D_ERR_LAUNCH = -7,        /* the CUDA runtime rejected a launch or a memset */
     M2D_ERR_ABI = -8,           /* descriptor size does not match this library */
-    M2D_ERR_TOO_LARGE = -9      /* problem exceeds a fixed capacity (no-allocation entry point) */
+    M2D_ERR_TOO_LARGE = -9      /* B*H*W*max(E, pitch) >= 2^31 (kernels use 31-bit element indices), or
+                                   scratch beyond the capacity of the no-allocation entry point */
 } m2d_status;
 
 /*

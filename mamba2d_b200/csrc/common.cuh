@@ -29,7 +29,65 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
+__device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
+    unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(s), "l"(gmem) : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Predicated forms (no branch, no reconvergence point): the copy / store happens iff `on`.
+__device__ __forceinline__ void cp_async16_if(bool on, unsigned smem_addr, const void* gmem) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0], [%1], 16;\n\t}"
+                 ::"r"(smem_addr), "l"(gmem), "r"((int)on) : "memory");
+}
+__device__ __forceinline__ void cp_async8_if(bool on, unsigned smem_addr, const void* gmem) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.ca.shared.global [%0], [%1], 8;\n\t}"
+                 ::"r"(smem_addr), "l"(gmem), "r"((int)on) : "memory");
+}
+__device__ __forceinline__ void stcg_if(bool on, float4* p, const float4& v) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t@p st.global.cg.v4.f32 [%0], {%1, %2, %3, %4};\n\t}"
+                 ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"((int)on) : "memory");
+}
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+
+// ---- input staging in shared memory ------------------------------------------------------------
+// Per warp and parity: 44 slots of 16 bytes: x[8] dT[8] dL[8] gy[8] (one slot per 4-channel block)
+// then BT[4] BL[4] C[4] (one slot per 4-state block).  A slot holds four elements of the I/O type
+// (fp32: 16 bytes, bf16: the first 8 bytes).
+constexpr int kStageSlots = 44;
+constexpr int kStageBytes = kStageSlots * 16;   // per parity
+
+// Asynchronous copy of four consecutive elements into a slot (vector path), or a guarded scalar
+// copy with zero fill (ragged path).
+template <bool VEC>
+__device__ __forceinline__ void stage4(bool on, char* slot, const float* __restrict__ p, int off, int nvalid) {
+    if (VEC) { cp_async16_if(on, smem_u32(slot), p + off); return; }
+    if (on) {
+        float* d = reinterpret_cast<float*>(slot);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) d[k] = (k < nvalid) ? __ldg(p + off + k) : 0.f;
+    }
+}
+template <bool VEC>
+__device__ __forceinline__ void stage4(bool on, char* slot, const __nv_bfloat16* __restrict__ p, int off, int nvalid) {
+    if (VEC) { cp_async8_if(on, smem_u32(slot), p + off); return; }
+    if (on) {
+        unsigned short* d = reinterpret_cast<unsigned short*>(slot);
+        const unsigned short* q = reinterpret_cast<const unsigned short*>(p) + off;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) d[k] = (k < nvalid) ? __ldg(q + k) : (unsigned short)0;
+    }
+}
+// Read a staged slot back as four floats.
+template <typename io_t> __device__ __forceinline__ float4 unstage4(const char* slot);
+template <> __device__ __forceinline__ float4 unstage4<float>(const char* slot) {
+    return *reinterpret_cast<const float4*>(slot);
+}
+template <> __device__ __forceinline__ float4 unstage4<__nv_bfloat16>(const char* slot) {
+    const uint2 u = *reinterpret_cast<const uint2*>(slot);
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                       __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+}
 
 // ---- element loads: four consecutive elements as floats, zero beyond `nvalid` ----------------
 template <bool VEC>

@@ -32,7 +32,8 @@ inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
 }
 
 inline Plan plan_bwd(const m2d_scan_desc* d) {
-    Plan p = plan_common(d, 8, 1);
+    Plan p = plan_common(d, 8, 8);
+    p.smem = bwd_smem_bytes(p.warps);
     p.scratch = bwd_layout(d, p).total;
     return p;
 }
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(256, 1) m2d_bwd_kernel(const ScanArgs a) {
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
 
-    const int total = 2 * (nwarps + 1) * kSlotF4;
+    const int total = (int)(bwd_smem_bytes(nwarps) / sizeof(float4));
     for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 
     float aT2[4][4], aL2[4][4];
@@ -155,8 +156,11 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     a.d_x = d->d_x; a.d_dT = d->d_dT; a.d_dL = d->d_dL;
     if (cudaMemsetAsync(ws + L.acc_begin, 0, L.total - L.acc_begin, st) != cudaSuccess) return M2D_ERR_LAUNCH;
     dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
-    if (vec) m2d_bwd_kernel<io_t, true><<<grid, block, pl.smem, st>>>(a);
-    else m2d_bwd_kernel<io_t, false><<<grid, block, pl.smem, st>>>(a);
+    auto kern = vec ? m2d_bwd_kernel<io_t, true> : m2d_bwd_kernel<io_t, false>;
+    if (pl.smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
+        return M2D_ERR_LAUNCH;
+    kern<<<grid, block, pl.smem, st>>>(a);
     if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
     const long long npix = (long long)d->B * d->H * d->W;
     const int fin_blocks = (int)((npix * d->N + 255) / 256 < 148 * 8 ? (npix * d->N + 255) / 256 : 148 * 8);

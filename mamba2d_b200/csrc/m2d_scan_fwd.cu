@@ -14,7 +14,7 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
 
-    const int total = 2 * ((blockDim.x >> 5) + 1) * kSlotF4;
+    const int total = (int)(sweep_smem_bytes(blockDim.x >> 5) / sizeof(float4));
     for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 
     float aT2[4][4], aL2[4][4];
@@ -40,8 +40,11 @@ static int launch_fwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     a.hs = nullptr;
     a.Rb = pl.Rb; a.nbands = pl.nbands;
     dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
-    if (vec) m2d_fwd_kernel<io_t, true><<<grid, block, pl.smem, st>>>(a);
-    else m2d_fwd_kernel<io_t, false><<<grid, block, pl.smem, st>>>(a);
+    auto kern = vec ? m2d_fwd_kernel<io_t, true> : m2d_fwd_kernel<io_t, false>;
+    if (pl.smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
+        return M2D_ERR_LAUNCH;
+    kern<<<grid, block, pl.smem, st>>>(a);
     return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
 }
 

@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_noalloc_kernel(const ScanArgs 
     const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
-    const int total = 2 * ((blockDim.x >> 5) + 1) * kSlotF4;
+    const int total = (int)(sweep_smem_bytes(blockDim.x >> 5) / sizeof(float4));
     for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     float aT2[4][4], aL2[4][4];
     load_param_block<io_t>(aT2, a.AT, a.N, ch0, chv, n0, nv, kLog2e);

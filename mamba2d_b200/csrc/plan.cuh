@@ -21,6 +21,14 @@ inline int check_desc(const m2d_scan_desc* d, bool bwd, bool need_ptrs) {
     if (d->B < 1 || d->E < 1 || d->N < 1 || d->H < 2 || d->W < 2) return M2D_ERR_SHAPE;
     if (d->N > kMaxN) return M2D_ERR_UNSUPPORTED_N;
     if (d->BT_pitch < d->N || d->BL_pitch < d->N || d->C_pitch < d->N) return M2D_ERR_PITCH;
+    {
+        // the kernels index every tensor with 31-bit element offsets
+        long long widest = d->E > 48 ? d->E : 48;
+        if (d->BT_pitch > widest) widest = d->BT_pitch;
+        if (d->BL_pitch > widest) widest = d->BL_pitch;
+        if (d->C_pitch > widest) widest = d->C_pitch;
+        if ((long long)d->B * d->H * d->W * widest >= (1ll << 31)) return M2D_ERR_TOO_LARGE;
+    }
     if (need_ptrs) {
         if (!d->x || !d->dT || !d->dL || !d->AT || !d->AL || !d->BT || !d->BL || !d->C || !d->D) return M2D_ERR_NULL;
         if (bwd && (!d->gy || !d->d_x || !d->d_dT || !d->d_dL || !d->d_AT || !d->d_AL || !d->d_BT || !d->d_BL || !d->d_C || !d->d_D))
@@ -41,17 +49,24 @@ inline bool vector_ok(const m2d_scan_desc* d, bool bwd) {
     return ok;
 }
 
+// Row-warps per CTA: as many as allowed, traded against rows lost to padding in the last band
+// (score = warps x fraction of useful rows; ties go to the better fraction).
 inline int pick_warps(int H, int max_warps) {
     if (H <= max_warps) return H;
-    int best = max_warps, best_waste = 1 << 30;
-    for (int w = max_warps; w >= (max_warps + 1) / 2 + 1; --w) {
-        const int waste = (H + w - 1) / w * w - H;
-        if (waste < best_waste) { best_waste = waste; best = w; }
+    int best = max_warps;
+    double best_score = -1.0, best_eff = 0.0;
+    for (int w = max_warps; w >= 2; --w) {
+        const int bands = (H + w - 1) / w;
+        const double eff = (double)H / ((double)bands * w);
+        const double score = w * eff;
+        if (score > best_score + 1e-9 || (score > best_score - 1e-9 && eff > best_eff)) {
+            best_score = score; best_eff = eff; best = w;
+        }
     }
     return best;
 }
 
-inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int ctas_per_sm) {
+inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int warps_per_sm) {
     Plan p;
     p.groups = (d->E + kGroup - 1) / kGroup;
     p.warps = pick_warps(d->H, max_warps);
@@ -63,11 +78,14 @@ inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int ctas_per_sm) 
         p.warps = p.Rb;
         p.nbands = (d->H + p.Rb - 1) / p.Rb;
     }
+    const int ctas_per_sm = warps_per_sm / p.warps > 0 ? warps_per_sm / p.warps : 1;
     const long long slots = (long long)ctas_per_sm * sm_count();
-    const long long units = (long long)d->B * p.groups;
-    const long long per = (units + slots - 1) / slots;          // images per CTA
+    // all CTAs resident at once: CTAs per channel group = floor(slots / groups), images per CTA to match
+    long long per_group = slots / p.groups;
+    if (per_group < 1) per_group = 1;
+    const long long per = (d->B + per_group - 1) / per_group;    // images per CTA
     p.grid_x = (int)((d->B + per - 1) / per);
-    p.smem = (size_t)2 * (p.warps + 1) * kSlotF4 * sizeof(float4);
+    p.smem = ((size_t)2 * (p.warps + 1) * kSlotF4 + (size_t)p.warps * 2 * kStageSlots) * sizeof(float4);
     p.scratch = 0;
     return p;
 }
@@ -75,7 +93,7 @@ inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int ctas_per_sm) 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 inline Plan plan_fwd(const m2d_scan_desc* d) {
-    Plan p = plan_common(d, 8, 2);
+    Plan p = plan_common(d, 8, 16);
     if (p.nbands > 1) p.scratch = align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
     return p;
 }

@@ -15,46 +15,34 @@
 //     d_x  = mT*dT*sum_n kap*BT + mL*dL*sum_n kap*BL + gy*D
 //     d_BT[n] = sum_e mT*kap*dT*x       d_BL[n] = sum_e mL*kap*dL*x        d_D[e] += gy*x
 // (d_C = sum_e gy*h is produced by the recompute sweep, where h is in registers.)
+// A missing neighbour is handled as in the forward sweep: its gate gets exponent -inf, so pT / pL
+// and with them dzT / dzL vanish on row 0 / column 0 without any masking of h.
 //
 // The sweep mirrors the forward one: bands are visited last to first, the bottom row of a band
-// leads, columns run right to left.  h comes from the state record the recompute sweep wrote.
+// leads (rank 0), columns run right to left; pT travels through the same shared-memory slots and
+// the same global ring.  h comes from the state record the recompute sweep wrote.  Every warp copies
+// h[i][j-1] of its own row into shared memory one step ahead (cp.async); the warp of the row below,
+// which runs one step ahead, needs exactly that block as its h[i-1][j] in the same step and reads
+// it from there, so each block crosses L2 -> SM once.  (The block h[i][W-1] is nobody's left
+// neighbour; the row's warp fetches it for the warp below one step before its own row starts.)
 #pragma once
 
 #include "sweep_fwd.cuh"
 
 namespace m2d {
 
-struct RevIn {
-    float4 x, dT, dL, gy, bT, bL, c;
-    float4 hl[4], ht[4];   // h[i][j-1] and h[i-1][j], one float4 (4 states) per channel
-};
+// Dynamic shared memory of the backward kernel: [hand-off slots][input stages][h areas], the h
+// areas being one per row-warp plus one for the row above the band.
+__host__ __device__ inline size_t bwd_smem_bytes(int warps) { return sweep_smem_bytes(warps) + handoff_bytes(warps); }
 
-template <typename io_t, bool VEC>
-__device__ __forceinline__ void load_rev(RevIn& ri, const ScanArgs& a, int b, int g, int i, int j, int lane, int ch0, int chv, int n0, int nv) {
-    const long long pix = ((long long)b * a.H + i) * a.W + j;
-    if (chv > 0) {   // see load_cell: never read beyond the last channel
-        ri.gy = load4<VEC>(static_cast<const io_t*>(a.gy), pix * a.E + ch0, chv);
-        ri.x = load4<VEC>(static_cast<const io_t*>(a.x), pix * a.E + ch0, chv);
-        ri.dT = load4<VEC>(static_cast<const io_t*>(a.dT), pix * a.E + ch0, chv);
-        ri.dL = load4<VEC>(static_cast<const io_t*>(a.dL), pix * a.E + ch0, chv);
-    } else {
-        ri.gy = ri.x = ri.dT = ri.dL = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    if (nv > 0) {
-        ri.bT = load4<VEC>(static_cast<const io_t*>(a.BT), pix * a.pBT + n0, nv);
-        ri.bL = load4<VEC>(static_cast<const io_t*>(a.BL), pix * a.pBL + n0, nv);
-        ri.c = load4<VEC>(static_cast<const io_t*>(a.C), pix * a.pC + n0, nv);
-    } else {
-        ri.bT = ri.bL = ri.c = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    const size_t rec = ((size_t)b * gridDim.y + g) * a.H * a.W + (size_t)i * a.W + j;
-    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        ri.hl[k] = (j > 0) ? __ldcg(a.hs + ((rec - 1) * 4 + k) * 32 + lane) : z;
-        ri.ht[k] = (i > 0) ? __ldcg(a.hs + ((rec - a.W) * 4 + k) * 32 + lane) : z;
-    }
-}
+struct RevRun {
+    int pixl, jl, ql;       // load side (reversed counters: jl = W-1-j, ql = nbands-1-q)
+    bool row_l, pull_l, top_l;
+    const float4* phl;      // state record of h[i][j-1] for the cell being staged
+    int pixc, jc, qc;       // compute side
+    bool row_c, push_c, bottom_c, row0_c;
+    float cfac, mT, mL, offT, offL;   // constants of the current cell class
+};
 
 // One CTA's adjoint sweep over image `b`.  dAT/dAL/dD accumulate across calls.
 template <typename io_t, bool VEC>
@@ -64,19 +52,32 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
-    const int g = blockIdx.y;
+    const int g = blockIdx.y, groups = gridDim.y;
     const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
-    const int W = a.W, H = a.H, Rb = a.Rb, nbands = a.nbands;
-    const int rr = Rb - 1 - r;                 // rank in the reverse sweep: the bottom row of a band leads
-    const int steps = nbands * W + Rb - 1;
-    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
-    float4* ring = a.ring + (size_t)cta * W * kSlotF4;
-    const int slot_stride = (nwarps + 1) * kSlotF4;
-
-    // destination of this lane's share of the channel sums (see the exchange below)
-    const bool hi16 = (cq & 4) != 0, hi8 = (cq & 2) != 0;
+    const int W = a.W, H = a.H, E = a.E, Rb = a.Rb, nbands = a.nbands;
+    const int rr = Rb - 1 - r;                 // rank in the reverse sweep
+    const int T = nbands * W;
+    const int steps = T + Rb - 1;
+    const int pBT = (int)a.pBT, pBL = (int)a.pBL, pC = (int)a.pC;
+    float4* const ring = a.ring + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * W) * kSlotF4 + lane;
+    float4* const my = handoff + rr * kSlotPair + lane;                       // pT: read slot rr, write slot rr+1
+    char* const stage = reinterpret_cast<char*>(handoff + (nwarps + 1) * kSlotPair) + r * 2 * kStageBytes;
+    float4* const harea = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes(nwarps)) + lane;
+    float4* const h_own = harea + (r + 1) * kSlotPair;                        // this row's h[i][j-1]
+    float4* const h_up = harea + r * kSlotPair;                               // the row above: h[i-1][j]
+    const float4* const hs_img = a.hs + ((size_t)b * groups + g) * H * W * kSlotF4 + lane;
+    const bool y_lane = (g * kGroup + lane) < E;
+    const bool ch_copier = (nq == 0) && (chv > 0);
+    const bool st_copier = (cq == 0) && (nv > 0);
+    const bool feeds_below = (r + 1 < Rb);     // a warp of this CTA owns the row below
+    const bool hi16 = (cq & 4) != 0, hi8 = (cq & 2) != 0, hi4 = (cq & 1) != 0;
+    const int db_n = n0 + (hi8 ? 2 : 0) + (hi4 ? 1 : 0);
+    const int db_off = (hi16 ? 16 : 0) + db_n;
+    const bool db_lane = db_n < a.N;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float ninf = __int_as_float(0xff800000);
 
     float pL[4][4];
 #pragma unroll
@@ -84,115 +85,157 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
 #pragma unroll
         for (int n = 0; n < 4; ++n) pL[c][n] = 0.f;
 
-    // positions are tracked in reversed coordinates (jr = W-1-j, qr = nbands-1-q)
-    Pos pn = {0, 0, 0};
-    bool vn = (rr == 0) && ((nbands - 1) * Rb + r < H);
-    RevIn nxt;
-    {
-        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-        nxt.x = nxt.dT = nxt.dL = nxt.gy = nxt.bT = nxt.bL = nxt.c = z;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) nxt.hl[k] = nxt.ht[k] = z;
-    }
-    if (vn) load_rev<io_t, VEC>(nxt, a, b, g, (nbands - 1) * Rb + r, W - 1, lane, ch0, chv, n0, nv);
+    RevRun st;
+    st.pixl = st.jl = st.ql = 0;
+    st.pixc = st.jc = st.qc = 0;
+    st.row_l = st.pull_l = st.top_l = st.row_c = st.push_c = st.bottom_c = st.row0_c = false;
+    st.phl = nullptr;
+    st.cfac = st.mT = st.mL = st.offT = st.offL = 0.f;
 
-    for (int s = 0; s < steps; ++s) {
-        const Pos pc = pn;
-        const bool vc = vn;
-        const RevIn cur = nxt;
-        float4* buf_w = handoff + (s & 1) * slot_stride;
-        const float4* buf_r = handoff + ((s & 1) ^ 1) * slot_stride;
-
-        if (s + 1 > rr) pn = advance(pc, W, nbands);
-        {
-            const int qn = nbands - 1 - pn.q;
-            const int in = qn * Rb + r, jn = W - 1 - pn.j;
-            vn = (s + 1 >= rr) && (pn.bi < 1) && (in < H);
-            if (vn) {
-                load_rev<io_t, VEC>(nxt, a, b, g, in, jn, lane, ch0, chv, n0, nv);
-                if (rr == 0 && in + 1 < H) {
-                    // the row below lives in the band visited before this one: pull its pT from the ring
+    // Fetch h[i][W-1] of the row this warp starts next, for the warp of the row below.
+    auto prefetch_row_end = [&](int q, int par) {
+        const int i = q * Rb + r;
+        if (feeds_below && r < Rb && i < H) {
+            const float4* src = hs_img + ((size_t)i * W + (W - 1)) * kSlotF4;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        cp_async16(buf_w + k * 32 + lane, ring + ((size_t)jn * 4 + k) * 32 + lane);
-                }
-            }
+            for (int k = 0; k < 4; ++k) cp_async16(h_own + par * kSlotF4 + k * 32, src + k * 32);
         }
+    };
 
-        if (vc) {
-            const int q = nbands - 1 - pc.q;
-            const int i = q * Rb + r, j = W - 1 - pc.j;
-            const long long pix = ((long long)b * H + i) * W + j;
-            const float cfac = (i > 0 && j > 0) ? 0.5f : 1.f;
-            const float mT = (i > 0) ? 1.f : 0.f;
-            const float mL = (j > 0 || i == 0) ? 1.f : 0.f;
-
-            float4 pd[4];   // pT of the row below
-            if (i + 1 < H) {
+    // ---- stage the inputs and h[i][j-1] (and h[i-1][j] for the top row of a band) of the next cell
+    auto load_phase = [&](int par) {
+        if (st.jl == 0) {   // start of a row (its right end)
+            const int q = nbands - 1 - st.ql;
+            const int i = q * Rb + r;
+            st.row_l = (r < Rb) && (i < H);
+            st.pull_l = st.row_l && (rr == 0) && (i + 1 < H);      // pT of the row below comes through the ring
+            st.top_l = st.row_l && (r == 0) && (i > 0);            // h of the row above is not in this band
+            st.pixl = (b * H + i) * W + (W - 1);
+            st.phl = hs_img + ((size_t)i * W + (W - 2)) * kSlotF4;
+        }
+        const int j = W - 1 - st.jl;
+        if (st.row_l) {
+            char* stg = stage + par * kStageBytes;
+            const int e0 = st.pixl * E + ch0;
+            stage4<VEC>(ch_copier, stg + cq * 16, static_cast<const io_t*>(a.x), e0, chv);
+            stage4<VEC>(ch_copier, stg + (8 + cq) * 16, static_cast<const io_t*>(a.dT), e0, chv);
+            stage4<VEC>(ch_copier, stg + (16 + cq) * 16, static_cast<const io_t*>(a.dL), e0, chv);
+            stage4<VEC>(ch_copier, stg + (24 + cq) * 16, static_cast<const io_t*>(a.gy), e0, chv);
+            stage4<VEC>(st_copier, stg + (32 + nq) * 16, static_cast<const io_t*>(a.BT), st.pixl * pBT + n0, nv);
+            stage4<VEC>(st_copier, stg + (36 + nq) * 16, static_cast<const io_t*>(a.BL), st.pixl * pBL + n0, nv);
+            stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), st.pixl * pC + n0, nv);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) pd[k] = buf_r[rr * kSlotF4 + k * 32 + lane];
-            } else {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) pd[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < 4; ++k) {
+                cp_async16_if(j > 0, smem_u32(h_own + par * kSlotF4 + k * 32), st.phl + k * 32);
+                cp_async16_if(st.top_l, smem_u32(h_up + par * kSlotF4 + k * 32), st.phl + (ptrdiff_t)(1 - W) * kSlotF4 + k * 32);
+                cp_async16_if(st.pull_l, smem_u32(my + par * kSlotF4 + k * 32), ring + j * kSlotF4 + k * 32);
             }
-            if (j == W - 1) {
+            --st.pixl;
+            st.phl -= kSlotF4;
+        }
+        // last cell of a row: its own h[i][-1] does not exist (that gate is zero), so the slot is
+        // free for the right-most block of the row this warp starts next
+        if (j == 0 && st.ql + 1 < nbands) prefetch_row_end(nbands - 2 - st.ql, par);
+        if (++st.jl == W) { st.jl = 0; ++st.ql; }
+    };
+
+    // ---- adjoint arithmetic of the current cell ---------------------------------------------------
+    auto compute_phase = [&](int par) {
+        if (st.jc == 0) {
+            const int q = nbands - 1 - st.qc;
+            const int i = q * Rb + r;
+            st.row_c = (r < Rb) && (i < H);
+            st.row0_c = (i == 0);
+            st.bottom_c = (i + 1 >= H);
+            st.push_c = st.row_c && (r == 0) && (q > 0);
+            st.pixc = (b * H + i) * W + (W - 1);
+            // columns j > 0: interior unless on row 0
+            st.cfac = st.row0_c ? 1.f : 0.5f;
+            st.mT = st.row0_c ? 0.f : 1.f;
+            st.mL = 1.f;
+            st.offT = st.row0_c ? ninf : 0.f;
+            st.offL = 0.f;
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
-                    for (int n = 0; n < 4; ++n) pL[c][n] = 0.f;
+                for (int n = 0; n < 4; ++n) pL[c][n] = 0.f;
+        }
+        if (st.row_c) {
+            const int j = W - 1 - st.jc;
+            if (j == 0) {   // column 0: no averaging, no left neighbour; the left input term exists only on row 0
+                st.cfac = 1.f;
+                st.mL = st.row0_c ? 1.f : 0.f;
+                st.offL = ninf;
             }
+            const float cfac = st.cfac, mT = st.mT, mL = st.mL;
+            const float2 offT2 = make_float2(st.offT, st.offT), offL2 = make_float2(st.offL, st.offL);
+            const char* stg = stage + (par ^ 1) * kStageBytes;
+            const float4 vx = unstage4<io_t>(stg + cq * 16);
+            const float4 vdT = unstage4<io_t>(stg + (8 + cq) * 16);
+            const float4 vdL = unstage4<io_t>(stg + (16 + cq) * 16);
+            const float4 vgy = unstage4<io_t>(stg + (24 + cq) * 16);
+            const float4 vbT = unstage4<io_t>(stg + (32 + nq) * 16);
+            const float4 vbL = unstage4<io_t>(stg + (36 + nq) * 16);
+            const float4 vc = unstage4<io_t>(stg + (40 + nq) * 16);
+            const float xs[4] = {vx.x, vx.y, vx.z, vx.w};
+            const float dTs[4] = {vdT.x, vdT.y, vdT.z, vdT.w};
+            const float dLs[4] = {vdL.x, vdL.y, vdL.z, vdL.w};
+            const float gys[4] = {vgy.x, vgy.y, vgy.z, vgy.w};
+            const float bTs[4] = {vbT.x, vbT.y, vbT.z, vbT.w};
+            const float bLs[4] = {vbL.x, vbL.y, vbL.z, vbL.w};
+            const float cs[4] = {vc.x, vc.y, vc.z, vc.w};
 
-            const float xs[4] = {cur.x.x, cur.x.y, cur.x.z, cur.x.w};
-            const float dTs[4] = {cur.dT.x, cur.dT.y, cur.dT.z, cur.dT.w};
-            const float dLs[4] = {cur.dL.x, cur.dL.y, cur.dL.z, cur.dL.w};
-            const float gys[4] = {cur.gy.x, cur.gy.y, cur.gy.z, cur.gy.w};
-            const float bTs[4] = {cur.bT.x, cur.bT.y, cur.bT.z, cur.bT.w};
-            const float bLs[4] = {cur.bL.x, cur.bL.y, cur.bL.z, cur.bL.w};
-            const float cs[4] = {cur.c.x, cur.c.y, cur.c.z, cur.c.w};
-
-            float dBT[4] = {0.f, 0.f, 0.f, 0.f}, dBL[4] = {0.f, 0.f, 0.f, 0.f};
+            float2 dBT2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            float2 dBL2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
             float o_dT[4], o_dL[4], o_dx[4];
-            float4 pTout[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const float hls[4] = {cur.hl[c].x, cur.hl[c].y, cur.hl[c].z, cur.hl[c].w};
-                const float hts[4] = {cur.ht[c].x, cur.ht[c].y, cur.ht[c].z, cur.ht[c].w};
-                const float pds[4] = {pd[c].x, pd[c].y, pd[c].z, pd[c].w};
+                const float4 hl4 = h_own[(par ^ 1) * kSlotF4 + c * 32];
+                const float4 ht4 = h_up[(par ^ 1) * kSlotF4 + c * 32];
+                const float4 pd4 = st.bottom_c ? zero4 : my[(par ^ 1) * kSlotF4 + c * 32];
+                const float hls[4] = {hl4.x, hl4.y, hl4.z, hl4.w};
+                const float hts[4] = {ht4.x, ht4.y, ht4.z, ht4.w};
+                const float pds[4] = {pd4.x, pd4.y, pd4.z, pd4.w};
                 const float wTc = mT * dTs[c] * xs[c];
                 const float wLc = mL * dLs[c] * xs[c];
                 const float gyc = cfac * gys[c];
-                float qT = 0.f, qL = 0.f, sT = 0.f, sL = 0.f;
+                float2 qT2 = make_float2(0.f, 0.f), qL2 = qT2, sT2 = qT2, sL2 = qT2;
                 float pt[4];
 #pragma unroll
-                for (int n = 0; n < 4; ++n) {
-                    const float kap = fmaf(gyc, cs[n], cfac * (pL[c][n] + pds[n]));
-                    const float gT = ex2(dTs[c] * aT2[c][n]);
-                    const float gL = ex2(dLs[c] * aL2[c][n]);
-                    const float pTn = gT * kap, pLn = gL * kap;
-                    const float dzT = pTn * hts[n], dzL = pLn * hls[n];
-                    dAT[c][n] = fmaf(dzT, dTs[c], dAT[c][n]);
-                    dAL[c][n] = fmaf(dzL, dLs[c], dAL[c][n]);
-                    qT = fmaf(dzT, aT2[c][n], qT);
-                    qL = fmaf(dzL, aL2[c][n], qL);
-                    sT = fmaf(kap, bTs[n], sT);
-                    sL = fmaf(kap, bLs[n], sL);
-                    dBT[n] = fmaf(kap, wTc, dBT[n]);
-                    dBL[n] = fmaf(kap, wLc, dBL[n]);
-                    pL[c][n] = pLn;
-                    pt[n] = pTn;
+                for (int n = 0; n < 4; n += 2) {
+                    const float2 aT = make_float2(aT2[c][n], aT2[c][n + 1]), aL = make_float2(aL2[c][n], aL2[c][n + 1]);
+                    const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), aT, offT2);
+                    const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), aL, offL2);
+                    const float2 gT = make_float2(ex2(argT.x), ex2(argT.y));
+                    const float2 gL = make_float2(ex2(argL.x), ex2(argL.y));
+                    const float2 in = __fmul2_rn(make_float2(cfac, cfac),
+                                                 __fadd2_rn(make_float2(pL[c][n], pL[c][n + 1]), make_float2(pds[n], pds[n + 1])));
+                    const float2 kap = __ffma2_rn(make_float2(gyc, gyc), make_float2(cs[n], cs[n + 1]), in);
+                    const float2 pTn = __fmul2_rn(gT, kap), pLn = __fmul2_rn(gL, kap);
+                    const float2 dzT = __fmul2_rn(pTn, make_float2(hts[n], hts[n + 1]));
+                    const float2 dzL = __fmul2_rn(pLn, make_float2(hls[n], hls[n + 1]));
+                    const float2 nAT = __ffma2_rn(dzT, make_float2(dTs[c], dTs[c]), make_float2(dAT[c][n], dAT[c][n + 1]));
+                    const float2 nAL = __ffma2_rn(dzL, make_float2(dLs[c], dLs[c]), make_float2(dAL[c][n], dAL[c][n + 1]));
+                    dAT[c][n] = nAT.x; dAT[c][n + 1] = nAT.y;
+                    dAL[c][n] = nAL.x; dAL[c][n + 1] = nAL.y;
+                    qT2 = __ffma2_rn(dzT, aT, qT2);
+                    qL2 = __ffma2_rn(dzL, aL, qL2);
+                    sT2 = __ffma2_rn(kap, make_float2(bTs[n], bTs[n + 1]), sT2);
+                    sL2 = __ffma2_rn(kap, make_float2(bLs[n], bLs[n + 1]), sL2);
+                    dBT2[n >> 1] = __ffma2_rn(kap, make_float2(wTc, wTc), dBT2[n >> 1]);
+                    dBL2[n >> 1] = __ffma2_rn(kap, make_float2(wLc, wLc), dBL2[n >> 1]);
+                    pL[c][n] = pLn.x; pL[c][n + 1] = pLn.y;
+                    pt[n] = pTn.x; pt[n + 1] = pTn.y;
                 }
-                pTout[c] = make_float4(pt[0], pt[1], pt[2], pt[3]);
+                // pT goes to the row above: next rank's slot, and the ring when that row is in another band
+                const float4 pT4 = make_float4(pt[0], pt[1], pt[2], pt[3]);
+                my[kSlotPair + par * kSlotF4 + c * 32] = pT4;
+                stcg_if(st.push_c, ring + j * kSlotF4 + c * 32, pT4);
+                const float qT = qT2.x + qT2.y, qL = qL2.x + qL2.y, sT = sT2.x + sT2.y, sL = sL2.x + sL2.y;
                 o_dT[c] = fmaf(qT, kLn2, mT * xs[c] * sT);
                 o_dL[c] = fmaf(qL, kLn2, mL * xs[c] * sL);
                 o_dx[c] = fmaf(mT * dTs[c], sT, mL * dLs[c] * sL);
                 dD[c] = fmaf(gys[c], xs[c], dD[c]);
-            }
-
-            // pT goes to the row above: next rank's slot, and the ring when that row is in another band
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                buf_w[(rr + 1) * kSlotF4 + c * 32 + lane] = pTout[c];
-                if (r == 0 && q > 0) __stcg(ring + ((size_t)j * 4 + c) * 32 + lane, pTout[c]);
             }
 
             // sums over states: 2-step exchange over the nq lanes; lane l ends with channel l of the group
@@ -200,16 +243,18 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 const float r_dT = reduce_states(o_dT[0], o_dT[1], o_dT[2], o_dT[3], nq);
                 const float r_dL = reduce_states(o_dL[0], o_dL[1], o_dL[2], o_dL[3], nq);
                 const float r_dx = reduce_states(o_dx[0], o_dx[1], o_dx[2], o_dx[3], nq);
-                const int ch = g * kGroup + lane;
-                if (ch < a.E) {
-                    store1(static_cast<io_t*>(a.d_dT), pix * a.E + ch, r_dT);
-                    store1(static_cast<io_t*>(a.d_dL), pix * a.E + ch, r_dL);
-                    store1(static_cast<io_t*>(a.d_x), pix * a.E + ch, fmaf(sel4(cur.gy, nq), D_own, r_dx));
+                if (y_lane) {
+                    const int eo = st.pixc * E + g * kGroup + lane;
+                    store1(static_cast<io_t*>(a.d_dT), eo, r_dT);
+                    store1(static_cast<io_t*>(a.d_dL), eo, r_dL);
+                    store1(static_cast<io_t*>(a.d_x), eo, fmaf(sel4(vgy, nq), D_own, r_dx));
                 }
             }
 
             // sums over channels: 8 values (d_BT[4], d_BL[4]) over the 8 cq lanes: 4 + 2 + 1 exchanges
             {
+                const float dBT[4] = {dBT2[0].x, dBT2[0].y, dBT2[1].x, dBT2[1].y};
+                const float dBL[4] = {dBL2[0].x, dBL2[0].y, dBL2[1].x, dBL2[1].y};
                 float k0 = hi16 ? dBL[0] : dBT[0], k1 = hi16 ? dBL[1] : dBT[1];
                 float k2 = hi16 ? dBL[2] : dBT[2], k3 = hi16 ? dBL[3] : dBT[3];
                 k0 += __shfl_xor_sync(0xffffffffu, hi16 ? dBT[0] : dBL[0], 16);
@@ -219,16 +264,34 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 float m0 = hi8 ? k2 : k0, m1 = hi8 ? k3 : k1;
                 m0 += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k2, 8);
                 m1 += __shfl_xor_sync(0xffffffffu, hi8 ? k1 : k3, 8);
-                const bool hi4 = (cq & 1) != 0;
                 float v = hi4 ? m1 : m0;
                 v += __shfl_xor_sync(0xffffffffu, hi4 ? m0 : m1, 4);
                 // this lane now owns array (hi16 ? d_BL : d_BT), state n0 + 2*hi8 + hi4
-                const int nn = n0 + (hi8 ? 2 : 0) + (hi4 ? 1 : 0);
-                if (nn < a.N) atomicAdd(a.accBC + pix * 48 + (hi16 ? 16 : 0) + nn, v);
+                if (db_lane) atomicAdd(a.accBC + ((long long)st.pixc * 48 + db_off), v);
             }
+            --st.pixc;
         }
+        if (++st.jc == W) { st.jc = 0; ++st.qc; }
+    };
+
+    // Step s: stage cell (s + 1 - rr), compute cell (s - rr); the step before a warp's first copy
+    // fetches the right-most block of its first row for the warp below.
+    int cl = -rr;
+    for (int s = -1; s < steps; s += 2) {
+        if ((unsigned)cl < (unsigned)T) load_phase(1);
+        else if (cl == -1) prefetch_row_end(nbands - 1, 1);
+        if ((unsigned)(cl - 1) < (unsigned)T) compute_phase(1);
+        ++cl;
         cp_async_wait_all();
         __syncthreads();
+        if (s + 1 < steps) {
+            if ((unsigned)cl < (unsigned)T) load_phase(0);
+            else if (cl == -1) prefetch_row_end(nbands - 1, 0);
+            if ((unsigned)(cl - 1) < (unsigned)T) compute_phase(0);
+            ++cl;
+            cp_async_wait_all();
+            __syncthreads();
+        }
     }
 }
 

@@ -9,11 +9,17 @@
 // The weights are folded into the exponent (exp2(dT*AT*log2e + log2 wT)), so a missing neighbour
 // costs nothing: its gate is exp2(-inf) = 0.
 //
-// Work decomposition: see Pos in common.cuh.  Warp r hands its fresh state to warp r+1 through a
-// double-buffered shared-memory slot; one __syncthreads per step keeps the warps in lock step.
-// The last row of a band reaches the first row of the next band (W - Rb + 1 steps later) through a
-// per-CTA ring in global memory that stays L2 resident; warp 0 pulls its slot back into shared
-// memory with cp.async one step ahead of use.
+// Work decomposition.  A CTA owns one 32-channel group and walks `nb` images; each image is cut
+// into `nbands` bands of `Rb` rows; warp r owns row q*Rb + r of band q and walks its W columns,
+// one per step, lagging r steps behind warp 0 so that the row above is always one step ahead (the
+// anti-diagonal wavefront).  Warp r hands its fresh state to warp r+1 through a double-buffered
+// shared-memory slot; one __syncthreads per step keeps the warps in lock step.  The last row of a
+// band reaches the first row of the next band (W - Rb + 1 steps later) through a per-CTA ring in
+// global memory; warp 0 pulls its slot back into shared memory with cp.async one step ahead of
+// use.  Inputs of the next cell are copied into a per-warp shared-memory stage with cp.async while
+// the current cell's arithmetic runs (one copy per distinct 16-byte piece, not per lane), and read
+// back from there a step later.  Addresses derive from one running 32-bit pixel index per side
+// (load / compute) that is recomputed only at the start of a row.
 #pragma once
 
 #include "common.cuh"
@@ -37,32 +43,18 @@ struct ScanArgs {
 };
 typedef ScanArgs FwdArgs;
 
-// Cell inputs held in registers (current step and the prefetched next step).
+// Shared-memory hand-off layout: [slot 0..warps][parity 0..1][4][32] float4.  Rank k reads slot k
+// and writes slot k+1; slot 0 receives the ring pull.
+constexpr int kSlotPair = 2 * kSlotF4;
+__host__ __device__ inline size_t handoff_bytes(int warps) { return (size_t)(warps + 1) * kSlotPair * sizeof(float4); }
+// Dynamic shared memory of a sweep: the hand-off slots followed by one input stage per warp.
+__host__ __device__ inline size_t sweep_smem_bytes(int warps) { return handoff_bytes(warps) + (size_t)warps * 2 * kStageBytes; }
+
+// Cell inputs held in registers.
 struct CellIn {
     float4 x, dT, dL, bT, bL, c;
     float4 gy;   // only loaded by the backward sweeps
 };
-
-template <typename io_t, bool VEC, bool WITH_GY>
-__device__ __forceinline__ void load_cell(CellIn& ci, const FwdArgs& a, long long pix, int ch0, int chv, int n0, int nv) {
-    // lanes whose channel block lies beyond E (last group of a width that is not a multiple of 32)
-    // must not touch memory: a vector load there would read the next pixel
-    if (chv > 0) {
-        if (WITH_GY) ci.gy = load4<VEC>(static_cast<const io_t*>(a.gy), pix * a.E + ch0, chv);
-        ci.x = load4<VEC>(static_cast<const io_t*>(a.x), pix * a.E + ch0, chv);
-        ci.dT = load4<VEC>(static_cast<const io_t*>(a.dT), pix * a.E + ch0, chv);
-        ci.dL = load4<VEC>(static_cast<const io_t*>(a.dL), pix * a.E + ch0, chv);
-    } else {
-        ci.gy = ci.x = ci.dT = ci.dL = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    if (nv > 0) {
-        ci.bT = load4<VEC>(static_cast<const io_t*>(a.BT), pix * a.pBT + n0, nv);
-        ci.bL = load4<VEC>(static_cast<const io_t*>(a.BL), pix * a.pBL + n0, nv);
-        ci.c = load4<VEC>(static_cast<const io_t*>(a.C), pix * a.pC + n0, nv);
-    } else {
-        ci.bT = ci.bL = ci.c = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-}
 
 // Load the thread's 4x4 block of a (E,N) parameter, scaled; zero outside the valid range.
 template <typename io_t>
@@ -74,24 +66,46 @@ __device__ __forceinline__ void load_param_block(float (&dst)[4][4], const void*
             dst[c][n] = (c < chv && n < nv) ? load1(static_cast<const io_t*>(P), (long long)(ch0 + c) * N + n0 + n) * scale : 0.f;
 }
 
-// One CTA's forward sweep over its work list.  `handoff` is shared memory of
-// 2 * (warps + 1) * kSlotF4 float4, zero-initialised by the caller.  With STORE_HS every fresh
-// state block is also written to a.hs.
+// Per-warp running state of a forward sweep.  Addresses are rebuilt every step from a running 32-bit
+// pixel index (one multiply-add each); the host guarantees that every element index fits 31 bits.
+struct FwdRun {
+    // ---- load side: the cell whose inputs are fetched next ----
+    int pixl;               // flat pixel index (b*H + i)*W + j
+    int jl, ql, bil;
+    bool row_l, pull_l;
+    // ---- compute side: the cell whose arithmetic runs now ----
+    int pixc;
+    float4* phs;            // state record of the current cell (recompute sweep only)
+    int jc, qc, bic;
+    bool row_c, row0_c, push_c;
+};
+
+// One CTA's forward sweep over images img0, img0 + img_stride, ... (nb of them).  `handoff` is
+// shared memory of handoff_bytes(warps), zero-initialised by the caller.  With STORE_HS every fresh
+// state block is also written to a.hs and d_C is accumulated (backward's recompute sweep).
 template <typename io_t, bool VEC, bool STORE_HS>
-__device__ __forceinline__ void forward_sweep(const FwdArgs& a, float4* handoff, const float (&aT2)[4][4],
+__device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff, const float (&aT2)[4][4],
                                               const float (&aL2)[4][4], float D_own, int img0, int img_stride, int nb) {
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
-    const int nwarps = blockDim.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
-    const int g = blockIdx.y;
+    const int g = blockIdx.y, groups = gridDim.y;
     const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
-    const int W = a.W, H = a.H, Rb = a.Rb, nbands = a.nbands;
-    const int steps = nb * nbands * W + Rb - 1;
-    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
-    float4* ring = a.ring + (size_t)cta * W * kSlotF4;
-    const int slot_stride = (nwarps + 1) * kSlotF4;   // float4 per parity buffer
+    const int W = a.W, H = a.H, E = a.E, Rb = a.Rb, nbands = a.nbands;
+    const int T = nb * nbands * W;            // cells in this warp's sequence
+    const int steps = T + Rb - 1;
+    const int pBT = (int)a.pBT, pBL = (int)a.pBL, pC = (int)a.pC;
+    float4* const ring = a.ring + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * W) * kSlotF4 + lane;
+    float4* const my = handoff + r * kSlotPair + lane;   // read slot r at my[par*128 + k*32], write slot r+1
+    char* const stage = reinterpret_cast<char*>(handoff + ((blockDim.x >> 5) + 1) * kSlotPair) + r * 2 * kStageBytes;
+    const bool y_lane = (g * kGroup + lane) < E;
+    const bool ch_copier = (nq == 0) && (chv > 0);   // lanes that copy per-channel / per-state inputs
+    const bool st_copier = (cq == 0) && (nv > 0);
+    const bool hi16 = (cq & 4) != 0, hi8 = (cq & 2) != 0;
+    const int dc_n = n0 + (hi16 ? 2 : 0) + (hi8 ? 1 : 0);
+    const bool dc_lane = ((cq & 1) == 0) && dc_n < a.N;
+    const float ninf = __int_as_float(0xff800000);
 
     float h[4][4];
 #pragma unroll
@@ -99,47 +113,82 @@ __device__ __forceinline__ void forward_sweep(const FwdArgs& a, float4* handoff,
 #pragma unroll
         for (int n = 0; n < 4; ++n) h[c][n] = 0.f;
 
-    Pos pn = {0, 0, 0};
-    bool vn = (r == 0) && (r < Rb) && (nb > 0);
-    CellIn nxt;
-    nxt.x = nxt.dT = nxt.dL = nxt.bT = nxt.bL = nxt.c = nxt.gy = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (vn) load_cell<io_t, VEC, STORE_HS>(nxt, a, (long long)img0 * H * W, ch0, chv, n0, nv);
+    FwdRun st;
+    st.jl = st.ql = st.bil = 0;
+    st.jc = st.qc = st.bic = 0;
+    st.row_l = st.pull_l = st.row_c = st.row0_c = st.push_c = false;
+    st.pixl = st.pixc = 0;
+    st.phs = nullptr;
 
-    for (int s = 0; s < steps; ++s) {
-        const Pos pc = pn;
-        const bool vc = vn;
-        const CellIn cur = nxt;
-        float4* buf_w = handoff + (s & 1) * slot_stride;          // written this step
-        const float4* buf_r = handoff + ((s & 1) ^ 1) * slot_stride;  // written last step
-
-        // ---- where this warp stands next step; prefetch its inputs --------------------------------
-        if (s + 1 > r) pn = advance(pc, W, nbands);
-        vn = (s + 1 >= r) && (r < Rb) && (pn.bi < nb) && (pn.q * Rb + r < H);
-        if (vn) {
-            const int bn = img0 + pn.bi * img_stride;
-            const long long pix = ((long long)bn * H + (pn.q * Rb + r)) * W + pn.j;
-            load_cell<io_t, VEC, STORE_HS>(nxt, a, pix, ch0, chv, n0, nv);
-            if (r == 0 && pn.q > 0) {
-                // row above lives in the previous band: pull it from the ring into slot 0
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    cp_async16(buf_w + k * 32 + lane, ring + ((size_t)pn.j * 4 + k) * 32 + lane);
-            }
+    // ---- issue the loads of the next cell of this warp's sequence into `nxt` -------------------
+    auto load_phase = [&](int par) {
+        if (st.jl == 0) {   // start of a row
+            const int i = st.ql * Rb + r;
+            const int b = img0 + st.bil * img_stride;
+            st.row_l = (r < Rb) && (i < H);
+            st.pull_l = st.row_l && (r == 0) && (st.ql > 0);
+            st.pixl = (b * H + i) * W;
         }
+        if (st.row_l) {
+            // one lane per distinct piece copies it: lanes nq == 0 the per-channel inputs of their
+            // block, lanes cq == 0 the per-state inputs.  Blocks beyond E or N are never copied
+            // (their slots stay zero): a vector copy there would read the next pixel.
+            char* stg = stage + par * kStageBytes;
+            {
+                const int e0 = st.pixl * E + ch0;
+                stage4<VEC>(ch_copier, stg + cq * 16, static_cast<const io_t*>(a.x), e0, chv);
+                stage4<VEC>(ch_copier, stg + (8 + cq) * 16, static_cast<const io_t*>(a.dT), e0, chv);
+                stage4<VEC>(ch_copier, stg + (16 + cq) * 16, static_cast<const io_t*>(a.dL), e0, chv);
+                if (STORE_HS) stage4<VEC>(ch_copier, stg + (24 + cq) * 16, static_cast<const io_t*>(a.gy), e0, chv);
+                stage4<VEC>(st_copier, stg + (32 + nq) * 16, static_cast<const io_t*>(a.BT), st.pixl * pBT + n0, nv);
+                stage4<VEC>(st_copier, stg + (36 + nq) * 16, static_cast<const io_t*>(a.BL), st.pixl * pBL + n0, nv);
+                stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), st.pixl * pC + n0, nv);
+            }
+            // the row above lives in the previous band: pull it from the ring into slot 0
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                cp_async16_if(st.pull_l, smem_u32(my + par * kSlotF4 + k * 32), ring + st.jl * kSlotF4 + k * 32);
+            ++st.pixl;
+        }
+        if (++st.jl == W) {
+            st.jl = 0;
+            if (++st.ql == nbands) { st.ql = 0; ++st.bil; }
+        }
+    };
 
-        if (vc) {
-            const int i = pc.q * Rb + r, j = pc.j;
-            const int b = img0 + pc.bi * img_stride;
-            const long long pix = ((long long)b * H + i) * W + j;
-            const float ninf = __int_as_float(0xff800000);
-            const float wT = (i == 0) ? 0.f : (j == 0 ? 1.f : 0.5f);
-            const float wL = (j == 0) ? (i == 0 ? 1.f : 0.f) : (i == 0 ? 1.f : 0.5f);
-            const float offT = (i == 0) ? ninf : (j == 0 ? 0.f : -1.f);
-            const float offL = (j == 0) ? ninf : (i == 0 ? 0.f : -1.f);
+    // ---- arithmetic of the current cell from `cur`; reads hand-off parity par^1, writes par ----
+    auto compute_phase = [&](int par) {
+        if (st.jc == 0) {
+            const int i = st.qc * Rb + r;
+            const int b = img0 + st.bic * img_stride;
+            st.row_c = (r < Rb) && (i < H);
+            st.row0_c = (i == 0);
+            st.push_c = st.row_c && (r == Rb - 1) && (st.qc < nbands - 1);
+            st.pixc = (b * H + i) * W;
+            if (STORE_HS) st.phs = a.hs + (((size_t)b * groups + g) * H * W + (size_t)i * W) * kSlotF4 + lane;
+        }
+        if (st.row_c) {
+            const bool first = (st.jc == 0);
+            const float wT = st.row0_c ? 0.f : (first ? 1.f : 0.5f);
+            const float wL = first ? (st.row0_c ? 1.f : 0.f) : (st.row0_c ? 1.f : 0.5f);
+            const float offT = st.row0_c ? ninf : (first ? 0.f : -1.f);
+            const float offL = first ? ninf : (st.row0_c ? 0.f : -1.f);
 
             float4 top[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) top[k] = buf_r[r * kSlotF4 + k * 32 + lane];
+            for (int k = 0; k < 4; ++k) top[k] = my[(par ^ 1) * kSlotF4 + k * 32];
+            CellIn cur;   // staged during the previous step
+            {
+                const char* stg = stage + (par ^ 1) * kStageBytes;
+                cur.x = unstage4<io_t>(stg + cq * 16);
+                cur.dT = unstage4<io_t>(stg + (8 + cq) * 16);
+                cur.dL = unstage4<io_t>(stg + (16 + cq) * 16);
+                if (STORE_HS) cur.gy = unstage4<io_t>(stg + (24 + cq) * 16);
+                else cur.gy = make_float4(0.f, 0.f, 0.f, 0.f);
+                cur.bT = unstage4<io_t>(stg + (32 + nq) * 16);
+                cur.bL = unstage4<io_t>(stg + (36 + nq) * 16);
+                cur.c = unstage4<io_t>(stg + (40 + nq) * 16);
+            }
 
             const float xs[4] = {cur.x.x, cur.x.y, cur.x.z, cur.x.w};
             const float dTs[4] = {cur.dT.x, cur.dT.y, cur.dT.z, cur.dT.w};
@@ -147,62 +196,88 @@ __device__ __forceinline__ void forward_sweep(const FwdArgs& a, float4* handoff,
             const float bTs[4] = {cur.bT.x, cur.bT.y, cur.bT.z, cur.bT.w};
             const float bLs[4] = {cur.bL.x, cur.bL.y, cur.bL.z, cur.bL.w};
             const float cs[4] = {cur.c.x, cur.c.y, cur.c.z, cur.c.w};
-            float yacc[4];
-            float dC[4] = {0.f, 0.f, 0.f, 0.f};   // backward only: sum over this thread's channels of gy*h
             const float gys[4] = {cur.gy.x, cur.gy.y, cur.gy.z, cur.gy.w};
+            float yacc[4];
+            float dC[4] = {0.f, 0.f, 0.f, 0.f};   // recompute sweep only: sum over this thread's channels of gy*h
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float tp[4] = {top[c].x, top[c].y, top[c].z, top[c].w};
                 const float dtx = wT * dTs[c] * xs[c];
                 const float dlx = wL * dLs[c] * xs[c];
-                float acc = 0.f;
+                // packed fp32x2 arithmetic (two states per instruction) everywhere except the exponentials
+                float2 acc2 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int n = 0; n < 4; ++n) {
-                    const float gT = ex2(fmaf(dTs[c], aT2[c][n], offT));
-                    const float gL = ex2(fmaf(dLs[c], aL2[c][n], offL));
-                    const float u = fmaf(dlx, bLs[n], dtx * bTs[n]);
-                    const float hn = fmaf(gL, h[c][n], fmaf(gT, tp[n], u));
-                    h[c][n] = hn;
-                    acc = fmaf(hn, cs[n], acc);
-                    if (STORE_HS) dC[n] = fmaf(gys[c], hn, dC[n]);
+                for (int n = 0; n < 4; n += 2) {
+                    const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), make_float2(aT2[c][n], aT2[c][n + 1]), make_float2(offT, offT));
+                    const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), make_float2(aL2[c][n], aL2[c][n + 1]), make_float2(offL, offL));
+                    const float2 gT = make_float2(ex2(argT.x), ex2(argT.y));
+                    const float2 gL = make_float2(ex2(argL.x), ex2(argL.y));
+                    const float2 u = __ffma2_rn(make_float2(dlx, dlx), make_float2(bLs[n], bLs[n + 1]),
+                                                __fmul2_rn(make_float2(dtx, dtx), make_float2(bTs[n], bTs[n + 1])));
+                    const float2 hn = __ffma2_rn(gL, make_float2(h[c][n], h[c][n + 1]),
+                                                 __ffma2_rn(gT, make_float2(tp[n], tp[n + 1]), u));
+                    h[c][n] = hn.x;
+                    h[c][n + 1] = hn.y;
+                    acc2 = __ffma2_rn(hn, make_float2(cs[n], cs[n + 1]), acc2);
+                    if (STORE_HS) {
+                        const float2 d2 = __ffma2_rn(make_float2(gys[c], gys[c]), hn, make_float2(dC[n], dC[n + 1]));
+                        dC[n] = d2.x;
+                        dC[n + 1] = d2.y;
+                    }
                 }
-                yacc[c] = acc;
+                yacc[c] = acc2.x + acc2.y;
             }
 
-            // hand the fresh state to the row below (slot r+1), to the next band, and to hs
+            // hand the fresh state to the row below (slot r+1), to the next band, and to the record
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float4 hv = make_float4(h[c][0], h[c][1], h[c][2], h[c][3]);
-                buf_w[(r + 1) * kSlotF4 + c * 32 + lane] = hv;
-                if (r == Rb - 1 && pc.q < nbands - 1) __stcg(ring + ((size_t)j * 4 + c) * 32 + lane, hv);
-                if (STORE_HS) {
-                    const size_t rec = ((size_t)b * gridDim.y + g) * H * W + (size_t)i * W + j;
-                    __stcg(a.hs + (rec * 4 + c) * 32 + lane, hv);
-                }
+                my[kSlotPair + par * kSlotF4 + c * 32] = hv;
+                if (STORE_HS) __stcg(st.phs + c * 32, hv);
             }
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                stcg_if(st.push_c, ring + st.jc * kSlotF4 + c * 32, make_float4(h[c][0], h[c][1], h[c][2], h[c][3]));
 
             if (STORE_HS) {
                 // d_C[pixel][n] = sum over channels of gy*h: finish over the 8 cq lanes, then one
                 // atomic per state from the even-cq lane of each pair
-                const bool hi16 = (cq & 4) != 0, hi8 = (cq & 2) != 0;
                 float k0 = hi16 ? dC[2] : dC[0], k1 = hi16 ? dC[3] : dC[1];
                 k0 += __shfl_xor_sync(0xffffffffu, hi16 ? dC[0] : dC[2], 16);
                 k1 += __shfl_xor_sync(0xffffffffu, hi16 ? dC[1] : dC[3], 16);
                 float k = hi8 ? k1 : k0;
                 k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
                 k += __shfl_xor_sync(0xffffffffu, k, 4);
-                const int nn = n0 + (hi16 ? 2 : 0) + (hi8 ? 1 : 0);
-                if ((cq & 1) == 0 && nn < a.N) atomicAdd(a.accBC + pix * 48 + 32 + nn, k);
-            }
-
-            if (a.y != nullptr) {
+                if (dc_lane) atomicAdd(a.accBC + ((long long)st.pixc * 48 + 32 + dc_n), k);
+                st.phs += kSlotF4;
+            } else {
                 const float ysum = reduce_states(yacc[0], yacc[1], yacc[2], yacc[3], nq);
-                const int ch = g * kGroup + lane;
-                if (ch < a.E) store1(static_cast<io_t*>(a.y), pix * a.E + ch, fmaf(sel4(cur.x, nq), D_own, ysum));
+                if (y_lane) store1(static_cast<io_t*>(a.y), st.pixc * E + g * kGroup + lane, fmaf(sel4(cur.x, nq), D_own, ysum));
             }
+            ++st.pixc;
         }
+        if (++st.jc == W) {
+            st.jc = 0;
+            if (++st.qc == nbands) { st.qc = 0; ++st.bic; }
+        }
+    };
+
+    // Step s: stage the inputs of cell (s + 1 - r), compute cell (s - r).  s runs from -1 so that the
+    // first copy has a step of its own.  Two steps per iteration keep the parity a constant.
+    int cl = -r;     // index of the cell staged in the current step
+    for (int s = -1; s < steps; s += 2) {
+        if ((unsigned)cl < (unsigned)T) load_phase(1);
+        if ((unsigned)(cl - 1) < (unsigned)T) compute_phase(1);
+        ++cl;
         cp_async_wait_all();
         __syncthreads();
+        if (s + 1 < steps) {
+            if ((unsigned)cl < (unsigned)T) load_phase(0);
+            if ((unsigned)(cl - 1) < (unsigned)T) compute_phase(0);
+            ++cl;
+            cp_async_wait_all();
+            __syncthreads();
+        }
     }
 }
 

@@ -55,7 +55,7 @@ def test_noalloc_rejects_problems_beyond_its_capacity():
     d = _lib.ScanDesc()
     d.struct_bytes = ctypes.sizeof(_lib.ScanDesc)
     d.dtype = _lib.M2D_F32
-    d.B, d.H, d.W, d.E, d.N = 128, 64, 4096, 64, 16          # ring: 256 CTAs x 4096 columns x 2 KiB = 2 GiB
+    d.B, d.H, d.W, d.E, d.N = 16, 64, 4096, 64, 16           # ring: 32 CTAs x 4096 columns x 2 KiB = 256 MiB
     d.BT_pitch = d.BL_pitch = d.C_pitch = 16
     assert L.m2d_scan_fwd_workspace(ctypes.byref(d)) > _lib.NOALLOC_SCRATCH_BYTES
     fake = ctypes.c_void_p(256)                               # never dereferenced: the size check comes first
