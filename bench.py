@@ -39,7 +39,7 @@ BYTES = {"f32": 4, "bf16": 2}
 
 # DRAM bytes (read + write) of ONE launch of the dominant kernel, from an ncu capture of this same
 # workload; see profiles/ for the capture summaries.  None = not captured for that dtype.
-NCU_TRAFFIC = {"f32": None, "bf16": None}
+NCU_TRAFFIC = {"f32": 6.456e9, "bf16": None}   # profiles/m2d_bwd_kernel_f32_D64_56x56.md
 
 
 def fwd_bytes(D, HW, s, B=BATCH, N=NSTATE):
@@ -270,7 +270,7 @@ def run_ours(args):
         "e2e": {"value": el * world * e2e_steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                 "note": "pinned host inputs -> device, fwd+bwd through the public API, y and all nine gradients -> pinned host"},
-        "gpu_launches": args.steps * len(STAGES) * 3,
+        "gpu_launches": args.steps * len(STAGES) * 3,   # per shape: forward kernel, backward kernel, cast kernel
         "roofline": {"bound": "hbm", "kernel": "m2d_bwd_kernel @ D=64,H=W=56,B=128", "achieved": dom_bytes / dom["bwd_ms"] / 1e6,
                      "peak": peak, "unit": "GB/s", "frac": dom_bytes / dom["bwd_ms"] / 1e6 / peak,
                      "peak_kind": peak_kind, "algorithmic_bytes": dom_bytes, "ms": dom["bwd_ms"],
@@ -287,7 +287,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def cpu_baseline(dtype, sample_batch=16, repeat=1, threads=None):
+def cpu_baseline(dtype, sample_batch=64, repeat=1, threads=None):
     """The C/OpenMP restatement (oracle/) timed on the host cores over a bounded sample: forward +
     backward of the four stage shapes at a reduced batch."""
     import torch

@@ -32,14 +32,14 @@ inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
 }
 
 inline Plan plan_bwd(const m2d_scan_desc* d) {
-    Plan p = plan_common(d, 8, 8);
+    Plan p = plan_common(d, 6, 12);
     p.smem = bwd_smem_bytes(p.warps);
     p.scratch = bwd_layout(d, p).total;
     return p;
 }
 
 template <typename io_t, bool VEC>
-__global__ void __launch_bounds__(256, 1) m2d_bwd_kernel(const ScanArgs a) {
+__global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
     extern __shared__ float4 handoff[];
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
