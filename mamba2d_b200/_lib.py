@@ -7,7 +7,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libm2d_scan.so")
+LIB_PATH = os.environ.get("M2D_SCAN_LIB", os.path.join(HERE, "libm2d_scan.so"))   # override: an alternative build of the same ABI
 
 M2D_F32, M2D_BF16 = 0, 1
 ABI_VERSION = 1

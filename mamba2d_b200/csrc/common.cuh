@@ -50,6 +50,28 @@ __device__ __forceinline__ void stcg_if(bool on, float4* p, const float4& v) {
 }
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 
+// Four 16-byte copies under one predicate: a 2 KiB (cell, warp) block, 512 bytes apart on both sides.
+__device__ __forceinline__ void cp_async16x4_if(bool on, unsigned smem_addr, const void* gmem) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t"
+        "@p cp.async.cg.shared.global [%0], [%1], 16;\n\t"
+        "@p cp.async.cg.shared.global [%0+512], [%1+512], 16;\n\t"
+        "@p cp.async.cg.shared.global [%0+1024], [%1+1024], 16;\n\t"
+        "@p cp.async.cg.shared.global [%0+1536], [%1+1536], 16;\n\t}"
+        ::"r"(smem_addr), "l"(gmem), "r"((int)on) : "memory");
+}
+// Four 16-byte stores (one 2 KiB block) under one predicate.
+__device__ __forceinline__ void stcg4_if(bool on, float4* p, const float4& v0, const float4& v1, const float4& v2, const float4& v3) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %17, 0;\n\t"
+        "@p st.global.cg.v4.f32 [%0], {%1, %2, %3, %4};\n\t"
+        "@p st.global.cg.v4.f32 [%0+512], {%5, %6, %7, %8};\n\t"
+        "@p st.global.cg.v4.f32 [%0+1024], {%9, %10, %11, %12};\n\t"
+        "@p st.global.cg.v4.f32 [%0+1536], {%13, %14, %15, %16};\n\t}"
+        ::"l"(p), "f"(v0.x), "f"(v0.y), "f"(v0.z), "f"(v0.w), "f"(v1.x), "f"(v1.y), "f"(v1.z), "f"(v1.w),
+          "f"(v2.x), "f"(v2.y), "f"(v2.z), "f"(v2.w), "f"(v3.x), "f"(v3.y), "f"(v3.z), "f"(v3.w), "r"((int)on) : "memory");
+}
+
 // ---- input staging in shared memory ------------------------------------------------------------
 // Per warp and parity: 44 slots of 16 bytes: x[8] dT[8] dL[8] gy[8] (one slot per 4-channel block)
 // then BT[4] BL[4] C[4] (one slot per 4-state block).  A slot holds four elements of the I/O type
@@ -78,6 +100,46 @@ __device__ __forceinline__ void stage4(bool on, char* slot, const __nv_bfloat16*
         for (int k = 0; k < 4; ++k) d[k] = (k < nvalid) ? __ldg(q + k) : (unsigned short)0;
     }
 }
+// Vector-path staging of one cell: every distinct piece of the seven input tensors is copied by
+// exactly one lane, with two instructions per warp.  Lanes 0..31 copy the per-channel tensors
+// (tensor = lane >> 3 of x, dT, dL, gy; piece = lane & 7, i.e. four channels); lanes 0..11 copy the
+// per-state tensors (tensor = lane >> 2 of BT, BL, C; piece = lane & 3).  The slot order of the
+// stage (x[8] dT[8] dL[8] gy[8] BT[4] BL[4] C[4]) makes the destination slot equal to the lane
+// (+32 for the second copy).  Pieces beyond E or N are never copied: their slots stay zero.
+template <typename io_t>
+struct LaneCopy {
+    const char* cbase;
+    const char* bbase;
+    int bpitch;
+    bool c_on, b_on;
+    __device__ __forceinline__ void init(const void* x, const void* dT, const void* dL, const void* gy, const void* BT,
+                                         const void* BL, const void* C, int pBT, int pBL, int pC, int E, int N, int g,
+                                         int lane, bool with_gy) {
+        const int t = lane >> 3, piece = lane & 7;
+        const void* cp = t == 0 ? x : (t == 1 ? dT : (t == 2 ? dL : gy));
+        const int ch = g * kGroup + piece * 4;
+        c_on = (ch < E) && (t < 3 || with_gy);
+        cbase = static_cast<const char*>(cp) + (size_t)ch * sizeof(io_t);
+        const int tb = lane >> 2, pb = lane & 3;
+        const void* bp = tb == 0 ? BT : (tb == 1 ? BL : C);
+        bpitch = tb == 0 ? pBT : (tb == 1 ? pBL : pC);
+        b_on = (lane < 12) && (pb * 4 < N);
+        bbase = static_cast<const char*>(bp) + (size_t)(pb * 4) * sizeof(io_t);
+    }
+    // stage_addr: shared-space address of the stage (this parity); pix: flat pixel index.
+    __device__ __forceinline__ void issue(unsigned stage_addr, int lane, int pix, int E) const {
+        const char* src_c = cbase + (size_t)(pix * E) * sizeof(io_t);
+        const char* src_b = bbase + (size_t)(pix * bpitch) * sizeof(io_t);
+        if (sizeof(io_t) == 4) {
+            cp_async16_if(c_on, stage_addr + lane * 16, src_c);
+            cp_async16_if(b_on, stage_addr + (32 + lane) * 16, src_b);
+        } else {
+            cp_async8_if(c_on, stage_addr + lane * 16, src_c);
+            cp_async8_if(b_on, stage_addr + (32 + lane) * 16, src_b);
+        }
+    }
+};
+
 // Read a staged slot back as four floats.
 template <typename io_t> __device__ __forceinline__ float4 unstage4(const char* slot);
 template <> __device__ __forceinline__ float4 unstage4<float>(const char* slot) {

@@ -33,7 +33,7 @@ inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
 
 inline Plan plan_bwd(const m2d_scan_desc* d) {
     Plan p = plan_common(d, 6, 12);
-    p.smem = bwd_smem_bytes(p.warps);
+    p.smem = bwd_smem_bytes(p.warps) + kParamF4 * sizeof(float4);
     p.scratch = bwd_layout(d, p).total;
     return p;
 }
@@ -52,9 +52,6 @@ __global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
     const int total = (int)(bwd_smem_bytes(nwarps) / sizeof(float4));
     for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 
-    float aT2[4][4], aL2[4][4];
-    load_param_block<io_t>(aT2, a.AT, a.N, ch0, chv, n0, nv, kLog2e);
-    load_param_block<io_t>(aL2, a.AL, a.N, ch0, chv, n0, nv, kLog2e);
     const int ch_own = g * kGroup + lane;
     const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
     float dAT[4][4], dAL[4][4], dD[4];
@@ -65,10 +62,13 @@ __global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
         for (int n = 0; n < 4; ++n) dAT[c][n] = dAL[c][n] = 0.f;
     }
     __syncthreads();
+    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + bwd_smem_bytes(nwarps));
+    if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane);
+    __syncthreads();
 
     for (int b = blockIdx.x; b < a.B; b += gridDim.x) {
-        forward_sweep<io_t, VEC, true>(a, handoff, aT2, aL2, D_own, b, 0, 1);
-        reverse_sweep<io_t, VEC>(a, handoff, aT2, aL2, D_own, dAT, dAL, dD, b);
+        forward_sweep<io_t, VEC, true>(a, handoff, params, D_own, b, 0, 1);
+        reverse_sweep<io_t, VEC>(a, handoff, params, D_own, dAT, dAL, dD, b);
     }
 
     // ---- per-(channel,state) sums: fold the CTA's row-warps through shared memory, then one

@@ -64,14 +64,14 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_noalloc_kernel(const ScanArgs 
     const int nv = min(4, max(0, a.N - n0));
     const int total = (int)(sweep_smem_bytes(blockDim.x >> 5) / sizeof(float4));
     for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float aT2[4][4], aL2[4][4];
-    load_param_block<io_t>(aT2, a.AT, a.N, ch0, chv, n0, nv, kLog2e);
-    load_param_block<io_t>(aL2, a.AL, a.N, ch0, chv, n0, nv, kLog2e);
     const int ch_own = g * kGroup + lane;
     const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
     __syncthreads();
+    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes((blockDim.x >> 5)));
+    if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane);
+    __syncthreads();
     const int nb = (a.B - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    forward_sweep<io_t, VEC, false>(a, handoff, aT2, aL2, D_own, blockIdx.x, gridDim.x, nb);
+    forward_sweep<io_t, VEC, false>(a, handoff, params, D_own, blockIdx.x, gridDim.x, nb);
 }
 
 template <typename io_t>
@@ -85,8 +85,11 @@ static int launch_noalloc(const m2d_scan_desc* d, const Plan& pl, bool vec, floa
     a.ring = ring;
     a.Rb = pl.Rb; a.nbands = pl.nbands;
     dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
-    if (vec) m2d_fwd_noalloc_kernel<io_t, true><<<grid, block, pl.smem, st>>>(a);
-    else m2d_fwd_noalloc_kernel<io_t, false><<<grid, block, pl.smem, st>>>(a);
+    auto kern = vec ? m2d_fwd_noalloc_kernel<io_t, true> : m2d_fwd_noalloc_kernel<io_t, false>;
+    if (pl.smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
+        return M2D_ERR_LAUNCH;
+    kern<<<grid, block, pl.smem, st>>>(a);
     return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
 }
 

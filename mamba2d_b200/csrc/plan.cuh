@@ -85,7 +85,7 @@ inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int warps_per_sm)
     if (per_group < 1) per_group = 1;
     const long long per = (d->B + per_group - 1) / per_group;    // images per CTA
     p.grid_x = (int)((d->B + per - 1) / per);
-    p.smem = ((size_t)2 * (p.warps + 1) * kSlotF4 + (size_t)p.warps * 2 * kStageSlots) * sizeof(float4);
+    p.smem = ((size_t)2 * (p.warps + 1) * kSlotF4 + (size_t)p.warps * 2 * kStageSlots + 256) * sizeof(float4);   // + parameters
     p.scratch = 0;
     return p;
 }

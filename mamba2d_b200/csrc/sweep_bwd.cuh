@@ -33,7 +33,7 @@ namespace m2d {
 
 // Dynamic shared memory of the backward kernel: [hand-off slots][input stages][h areas], the h
 // areas being one per row-warp plus one for the row above the band.
-__host__ __device__ inline size_t bwd_smem_bytes(int warps) { return sweep_smem_bytes(warps) + handoff_bytes(warps); }
+__host__ __device__ inline size_t bwd_smem_bytes(int warps) { return sweep_smem_bytes(warps) + handoff_bytes(warps); }   // + parameters behind
 
 struct RevRun {
     int pixl, jl, ql;       // load side (reversed counters: jl = W-1-j, ql = nbands-1-q)
@@ -46,8 +46,8 @@ struct RevRun {
 
 // One CTA's adjoint sweep over image `b`.  dAT/dAL/dD accumulate across calls.
 template <typename io_t, bool VEC>
-__device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff, const float (&aT2)[4][4],
-                                              const float (&aL2)[4][4], float D_own, float (&dAT)[4][4],
+__device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff, const float4* params,
+                                              float D_own, float (&dAT)[4][4],
                                               float (&dAL)[4][4], float (&dD)[4], int b) {
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
@@ -85,6 +85,9 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
 #pragma unroll
         for (int n = 0; n < 4; ++n) pL[c][n] = 0.f;
 
+    LaneCopy<io_t> lc;
+    lc.init(a.x, a.dT, a.dL, a.gy, a.BT, a.BL, a.C, pBT, pBL, pC, E, a.N, g, lane, true);
+
     RevRun st;
     st.pixl = st.jl = st.ql = 0;
     st.pixc = st.jc = st.qc = 0;
@@ -97,8 +100,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
         const int i = q * Rb + r;
         if (feeds_below && r < Rb && i < H) {
             const float4* src = hs_img + ((size_t)i * W + (W - 1)) * kSlotF4;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) cp_async16(h_own + par * kSlotF4 + k * 32, src + k * 32);
+            cp_async16x4_if(true, smem_u32(h_own + par * kSlotF4), src);
         }
     };
 
@@ -116,20 +118,21 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
         const int j = W - 1 - st.jl;
         if (st.row_l) {
             char* stg = stage + par * kStageBytes;
-            const int e0 = st.pixl * E + ch0;
-            stage4<VEC>(ch_copier, stg + cq * 16, static_cast<const io_t*>(a.x), e0, chv);
-            stage4<VEC>(ch_copier, stg + (8 + cq) * 16, static_cast<const io_t*>(a.dT), e0, chv);
-            stage4<VEC>(ch_copier, stg + (16 + cq) * 16, static_cast<const io_t*>(a.dL), e0, chv);
-            stage4<VEC>(ch_copier, stg + (24 + cq) * 16, static_cast<const io_t*>(a.gy), e0, chv);
-            stage4<VEC>(st_copier, stg + (32 + nq) * 16, static_cast<const io_t*>(a.BT), st.pixl * pBT + n0, nv);
-            stage4<VEC>(st_copier, stg + (36 + nq) * 16, static_cast<const io_t*>(a.BL), st.pixl * pBL + n0, nv);
-            stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), st.pixl * pC + n0, nv);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                cp_async16_if(j > 0, smem_u32(h_own + par * kSlotF4 + k * 32), st.phl + k * 32);
-                cp_async16_if(st.top_l, smem_u32(h_up + par * kSlotF4 + k * 32), st.phl + (ptrdiff_t)(1 - W) * kSlotF4 + k * 32);
-                cp_async16_if(st.pull_l, smem_u32(my + par * kSlotF4 + k * 32), ring + j * kSlotF4 + k * 32);
+            if (VEC) {
+                lc.issue(smem_u32(stg), lane, st.pixl, E);
+            } else {
+                const int e0 = st.pixl * E + ch0;
+                stage4<VEC>(ch_copier, stg + cq * 16, static_cast<const io_t*>(a.x), e0, chv);
+                stage4<VEC>(ch_copier, stg + (8 + cq) * 16, static_cast<const io_t*>(a.dT), e0, chv);
+                stage4<VEC>(ch_copier, stg + (16 + cq) * 16, static_cast<const io_t*>(a.dL), e0, chv);
+                stage4<VEC>(ch_copier, stg + (24 + cq) * 16, static_cast<const io_t*>(a.gy), e0, chv);
+                stage4<VEC>(st_copier, stg + (32 + nq) * 16, static_cast<const io_t*>(a.BT), st.pixl * pBT + n0, nv);
+                stage4<VEC>(st_copier, stg + (36 + nq) * 16, static_cast<const io_t*>(a.BL), st.pixl * pBL + n0, nv);
+                stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), st.pixl * pC + n0, nv);
             }
+            cp_async16x4_if(j > 0, smem_u32(h_own + par * kSlotF4), st.phl);
+            cp_async16x4_if(st.top_l, smem_u32(h_up + par * kSlotF4), st.phl + (ptrdiff_t)(1 - W) * kSlotF4);
+            cp_async16x4_if(st.pull_l, smem_u32(my + par * kSlotF4), ring + j * kSlotF4);
             --st.pixl;
             st.phl -= kSlotF4;
         }
@@ -196,6 +199,8 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 const float hls[4] = {hl4.x, hl4.y, hl4.z, hl4.w};
                 const float hts[4] = {ht4.x, ht4.y, ht4.z, ht4.w};
                 const float pds[4] = {pd4.x, pd4.y, pd4.z, pd4.w};
+                const float4 qa = params[c * 32 + lane], qb = params[128 + c * 32 + lane];
+                const float aT2c[4] = {qa.x, qa.y, qa.z, qa.w}, aL2c[4] = {qb.x, qb.y, qb.z, qb.w};
                 const float wTc = mT * dTs[c] * xs[c];
                 const float wLc = mL * dLs[c] * xs[c];
                 const float gyc = cfac * gys[c];
@@ -203,7 +208,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 float pt[4];
 #pragma unroll
                 for (int n = 0; n < 4; n += 2) {
-                    const float2 aT = make_float2(aT2[c][n], aT2[c][n + 1]), aL = make_float2(aL2[c][n], aL2[c][n + 1]);
+                    const float2 aT = make_float2(aT2c[n], aT2c[n + 1]), aL = make_float2(aL2c[n], aL2c[n + 1]);
                     const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), aT, offT2);
                     const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), aL, offL2);
                     const float2 gT = make_float2(ex2(argT.x), ex2(argT.y));

@@ -49,6 +49,24 @@ constexpr int kSlotPair = 2 * kSlotF4;
 __host__ __device__ inline size_t handoff_bytes(int warps) { return (size_t)(warps + 1) * kSlotPair * sizeof(float4); }
 // Dynamic shared memory of a sweep: the hand-off slots followed by one input stage per warp.
 __host__ __device__ inline size_t sweep_smem_bytes(int warps) { return handoff_bytes(warps) + (size_t)warps * 2 * kStageBytes; }
+// The per-(channel,state) parameters A*log2(e) of the CTA's 32 channels live in shared memory
+// behind everything else: [AT | AL][4 channels][32 lanes] float4 (4 KiB), read block by block.
+constexpr int kParamF4 = 2 * 4 * 32;
+template <typename io_t>
+__device__ __forceinline__ void stage_params(float4* dst, const void* AT, const void* AL, int N, int ch0, int chv, int n0, int nv, int lane) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        float t[4], l[4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const bool ok = (c < chv) && (n < nv);
+            t[n] = ok ? load1(static_cast<const io_t*>(AT), (long long)(ch0 + c) * N + n0 + n) * kLog2e : 0.f;
+            l[n] = ok ? load1(static_cast<const io_t*>(AL), (long long)(ch0 + c) * N + n0 + n) * kLog2e : 0.f;
+        }
+        dst[c * 32 + lane] = make_float4(t[0], t[1], t[2], t[3]);
+        dst[128 + c * 32 + lane] = make_float4(l[0], l[1], l[2], l[3]);
+    }
+}
 
 // Cell inputs held in registers.
 struct CellIn {
@@ -84,8 +102,8 @@ struct FwdRun {
 // shared memory of handoff_bytes(warps), zero-initialised by the caller.  With STORE_HS every fresh
 // state block is also written to a.hs and d_C is accumulated (backward's recompute sweep).
 template <typename io_t, bool VEC, bool STORE_HS>
-__device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff, const float (&aT2)[4][4],
-                                              const float (&aL2)[4][4], float D_own, int img0, int img_stride, int nb) {
+__device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff, const float4* params,
+                                              float D_own, int img0, int img_stride, int nb) {
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
     const int g = blockIdx.y, groups = gridDim.y;
@@ -113,6 +131,9 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
 #pragma unroll
         for (int n = 0; n < 4; ++n) h[c][n] = 0.f;
 
+    LaneCopy<io_t> lc;
+    lc.init(a.x, a.dT, a.dL, a.gy, a.BT, a.BL, a.C, pBT, pBL, pC, E, a.N, g, lane, STORE_HS);
+
     FwdRun st;
     st.jl = st.ql = st.bil = 0;
     st.jc = st.qc = st.bic = 0;
@@ -130,11 +151,11 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
             st.pixl = (b * H + i) * W;
         }
         if (st.row_l) {
-            // one lane per distinct piece copies it: lanes nq == 0 the per-channel inputs of their
-            // block, lanes cq == 0 the per-state inputs.  Blocks beyond E or N are never copied
-            // (their slots stay zero): a vector copy there would read the next pixel.
             char* stg = stage + par * kStageBytes;
-            {
+            if (VEC) {
+                lc.issue(smem_u32(stg), lane, st.pixl, E);
+            } else {
+                // ragged shapes: one lane per distinct piece, guarded scalar copies (see LaneCopy)
                 const int e0 = st.pixl * E + ch0;
                 stage4<VEC>(ch_copier, stg + cq * 16, static_cast<const io_t*>(a.x), e0, chv);
                 stage4<VEC>(ch_copier, stg + (8 + cq) * 16, static_cast<const io_t*>(a.dT), e0, chv);
@@ -145,9 +166,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                 stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), st.pixl * pC + n0, nv);
             }
             // the row above lives in the previous band: pull it from the ring into slot 0
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-                cp_async16_if(st.pull_l, smem_u32(my + par * kSlotF4 + k * 32), ring + st.jl * kSlotF4 + k * 32);
+            cp_async16x4_if(st.pull_l, smem_u32(my + par * kSlotF4), ring + st.jl * kSlotF4);
             ++st.pixl;
         }
         if (++st.jl == W) {
@@ -202,14 +221,16 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float tp[4] = {top[c].x, top[c].y, top[c].z, top[c].w};
+                const float4 pT4 = params[c * 32 + lane], pL4 = params[128 + c * 32 + lane];
+                const float aT2c[4] = {pT4.x, pT4.y, pT4.z, pT4.w}, aL2c[4] = {pL4.x, pL4.y, pL4.z, pL4.w};
                 const float dtx = wT * dTs[c] * xs[c];
                 const float dlx = wL * dLs[c] * xs[c];
                 // packed fp32x2 arithmetic (two states per instruction) everywhere except the exponentials
                 float2 acc2 = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int n = 0; n < 4; n += 2) {
-                    const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), make_float2(aT2[c][n], aT2[c][n + 1]), make_float2(offT, offT));
-                    const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), make_float2(aL2[c][n], aL2[c][n + 1]), make_float2(offL, offL));
+                    const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), make_float2(aT2c[n], aT2c[n + 1]), make_float2(offT, offT));
+                    const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), make_float2(aL2c[n], aL2c[n + 1]), make_float2(offL, offL));
                     const float2 gT = make_float2(ex2(argT.x), ex2(argT.y));
                     const float2 gL = make_float2(ex2(argL.x), ex2(argL.y));
                     const float2 u = __ffma2_rn(make_float2(dlx, dlx), make_float2(bLs[n], bLs[n + 1]),
@@ -229,15 +250,14 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
             }
 
             // hand the fresh state to the row below (slot r+1), to the next band, and to the record
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float4 hv = make_float4(h[c][0], h[c][1], h[c][2], h[c][3]);
-                my[kSlotPair + par * kSlotF4 + c * 32] = hv;
-                if (STORE_HS) __stcg(st.phs + c * 32, hv);
+            {
+                const float4 h0 = make_float4(h[0][0], h[0][1], h[0][2], h[0][3]), h1 = make_float4(h[1][0], h[1][1], h[1][2], h[1][3]);
+                const float4 h2 = make_float4(h[2][0], h[2][1], h[2][2], h[2][3]), h3 = make_float4(h[3][0], h[3][1], h[3][2], h[3][3]);
+                float4* dst = my + kSlotPair + par * kSlotF4;
+                dst[0] = h0; dst[32] = h1; dst[64] = h2; dst[96] = h3;
+                stcg4_if(st.push_c, ring + st.jc * kSlotF4, h0, h1, h2, h3);
+                if (STORE_HS) stcg4_if(true, st.phs, h0, h1, h2, h3);
             }
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                stcg_if(st.push_c, ring + st.jc * kSlotF4 + c * 32, make_float4(h[c][0], h[c][1], h[c][2], h[c][3]));
 
             if (STORE_HS) {
                 // d_C[pixel][n] = sum over channels of gy*h: finish over the 8 cq lanes, then one
