@@ -282,6 +282,8 @@ def run_ours(args):
     }
     if world == 1 and not args.no_cpu:
         out["cpu_baseline"] = cpu_baseline(args.dtype)
+    if world == 1 and not args.no_ref_gpu:
+        out["reference_gpu"] = reference_gpu(devin, args.dtype)
     print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -312,6 +314,43 @@ def cpu_baseline(dtype, sample_batch=64, repeat=1, threads=None):
             "sample": f"fwd+bwd of the four stage shapes at batch {sample_batch} (of 128), fp32 arithmetic, "
                       f"{repeat} pass(es), {t:.1f} s wall on {cores} threads",
             "seconds": t}
+
+
+def reference_gpu(devin, dtype, iters=2):
+    """The reference project's own CUDA extension (built unmodified into oracle/_ref/, sm_100) with its
+    PyTorch glue restated in oracle/ref_gpu.py, timed on this GPU on the same inputs: forward + backward of
+    the four stage shapes.  Reported beside our numbers; it is the GPU implementation being replaced."""
+    import torch
+    try:
+        from oracle import ref_gpu
+        if not ref_gpu.available():
+            return {"unavailable": "oracle/_ref/wf_ref_cuda.so not prebuilt"}
+        per, total = [], 0.0
+        for (D, HW), d in zip(STAGES, devin):
+            a = [d[k].contiguous() for k in ORDER]
+            gy = d["gy"]
+            ref_gpu.forward(*a)
+            ref_gpu.backward(*a, gy)
+            torch.cuda.synchronize()
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            f = b = 0.0
+            for _ in range(iters):
+                e[0].record()
+                ref_gpu.forward(*a)
+                e[1].record()
+                ref_gpu.backward(*a, gy)
+                e[2].record()
+                torch.cuda.synchronize()
+                f += e[0].elapsed_time(e[1]) / iters
+                b += e[1].elapsed_time(e[2]) / iters
+            per.append({"D": D, "HW": HW, "fwd_ms": round(f, 3), "bwd_ms": round(b, 3)})
+            total += f + b
+            torch.cuda.empty_cache()
+        return {"value": elements() / (total * 1e-3), "unit": UNIT, "ms_per_step": total, "per_shape": per,
+                "what": "reference wf_cuda extension (one launch per anti-diagonal) + its PyTorch readout / gradient math, "
+                        "same GPU, same inputs (B/C made contiguous), device-resident, CUDA events"}
+    except Exception as exc:   # the baseline is informative only
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
 
 
 def run_reference(args):
@@ -348,6 +387,7 @@ def main():
     ap.add_argument("--dtype", choices=("f32", "bf16"), default="f32")
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline leg")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's CUDA extension")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
