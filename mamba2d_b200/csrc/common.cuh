@@ -60,6 +60,19 @@ __device__ __forceinline__ void cp_async16x4_if(bool on, unsigned smem_addr, con
         "@p cp.async.cg.shared.global [%0+1536], [%1+1536], 16;\n\t}"
         ::"r"(smem_addr), "l"(gmem), "r"((int)on) : "memory");
 }
+// Two 16-byte copies under one predicate: a 1 KiB (cell, warp) block of bf16 states.
+__device__ __forceinline__ void cp_async16x2_if(bool on, unsigned smem_addr, const void* gmem) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t"
+        "@p cp.async.cg.shared.global [%0], [%1], 16;\n\t"
+        "@p cp.async.cg.shared.global [%0+512], [%1+512], 16;\n\t}"
+        ::"r"(smem_addr), "l"(gmem), "r"((int)on) : "memory");
+}
+__device__ __forceinline__ unsigned pack_bf16x2(float lo, float hi) {
+    unsigned r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 // Four 16-byte stores (one 2 KiB block) under one predicate.
 __device__ __forceinline__ void stcg4_if(bool on, float4* p, const float4& v0, const float4& v1, const float4& v2, const float4& v3) {
     asm volatile(

@@ -8,25 +8,27 @@ namespace m2d {
 // Workspace layout of the backward pass (all regions 256-byte aligned):
 //   hs     state record written by the recompute sweep     B*groups*H*W*2 KiB
 //   ring   per-CTA band-boundary ring                      ctas*W*2 KiB   (only if nbands > 1)
-//   acc    fp32 accumulators: [B*H*W][48] | [2][E][N] | [E]   (zeroed before the main kernel)
+//   acc    bf16 I/O only: fp32 accumulators 3 x [B*H*W][N] | 2 x [E][N] | [E], zeroed before the
+//          main kernel and cast by a second kernel.  With fp32 I/O the kernel accumulates straight
+//          into the caller's (zeroed) gradient tensors and this region is empty.
 struct BwdLayout {
-    size_t hs, ring, accBC, accA, accD, total, acc_begin;
+    size_t hs, ring, acc, acc_bytes, total;
 };
 
 inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
     BwdLayout L;
     size_t off = 0;
     L.hs = off;
-    off += align256((size_t)d->B * p.groups * d->H * d->W * kSlotF4 * sizeof(float4));
+    off += align256((size_t)d->B * p.groups * d->H * d->W * (d->dtype == M2D_F32 ? 128 : 64) * sizeof(float4));
     L.ring = off;
     if (p.nbands > 1) off += align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
-    L.acc_begin = off;
-    L.accBC = off;
-    off += align256((size_t)d->B * d->H * d->W * 48 * sizeof(float));
-    L.accA = off;
-    off += align256((size_t)2 * d->E * d->N * sizeof(float));
-    L.accD = off;
-    off += align256((size_t)d->E * sizeof(float));
+    L.acc = off;
+    L.acc_bytes = 0;
+    if (d->dtype != M2D_F32) {
+        const size_t npn = (size_t)d->B * d->H * d->W * d->N, en = (size_t)d->E * d->N;
+        L.acc_bytes = align256((3 * npn + 2 * en + d->E) * sizeof(float));
+    }
+    off += L.acc_bytes;
     L.total = off;
     return L;
 }
@@ -104,8 +106,8 @@ __global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
                     if (n < nv) {
-                        atomicAdd(a.accA + (size_t)(ch0 + c) * a.N + n0 + n, dAT[c][n]);
-                        atomicAdd(a.accA + (size_t)a.E * a.N + (size_t)(ch0 + c) * a.N + n0 + n, dAL[c][n]);
+                        atomicAdd(a.accAT + (size_t)(ch0 + c) * a.N + n0 + n, dAT[c][n]);
+                        atomicAdd(a.accAL + (size_t)(ch0 + c) * a.N + n0 + n, dAL[c][n]);
                     }
                 }
                 if (nq == 0) atomicAdd(a.accD + ch0 + c, dD[c]);
@@ -114,26 +116,23 @@ __global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
     }
 }
 
-// Cast the fp32 accumulators into the caller's gradient tensors.
+// bf16 I/O: cast the fp32 accumulators into the caller's gradient tensors.
 template <typename io_t>
-__global__ void m2d_bwd_finalize(const float* __restrict__ accBC, const float* __restrict__ accA, const float* __restrict__ accD,
-                                 io_t* d_BT, io_t* d_BL, io_t* d_C, io_t* d_AT, io_t* d_AL, io_t* d_D,
-                                 long long npix, int N, int E) {
+__global__ void m2d_bwd_finalize(const float* __restrict__ acc, io_t* d_BT, io_t* d_BL, io_t* d_C, io_t* d_AT, io_t* d_AL,
+                                 io_t* d_D, long long npn, long long en, int E) {
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long nthreads = (long long)gridDim.x * blockDim.x;
-    const long long tot = npix * N;
-    for (long long k = tid; k < tot; k += nthreads) {
-        const long long p = k / N;
-        const int n = (int)(k - p * N);
-        store1(d_BT, k, accBC[p * 48 + n]);
-        store1(d_BL, k, accBC[p * 48 + 16 + n]);
-        store1(d_C, k, accBC[p * 48 + 32 + n]);
+    for (long long k = tid; k < npn; k += nthreads) {
+        store1(d_BT, k, acc[k]);
+        store1(d_BL, k, acc[npn + k]);
+        store1(d_C, k, acc[2 * npn + k]);
     }
-    for (long long k = tid; k < (long long)E * N; k += nthreads) {
+    const float* accA = acc + 3 * npn;
+    for (long long k = tid; k < en; k += nthreads) {
         store1(d_AT, k, accA[k]);
-        store1(d_AL, k, accA[(long long)E * N + k]);
+        store1(d_AL, k, accA[en + k]);
     }
-    for (long long k = tid; k < E; k += nthreads) store1(d_D, k, accD[k]);
+    for (long long k = tid; k < E; k += nthreads) store1(d_D, k, accA[2 * en + k]);
 }
 
 template <typename io_t>
@@ -150,11 +149,21 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     a.Rb = pl.Rb; a.nbands = pl.nbands;
     a.gy = d->gy;
     a.hs = reinterpret_cast<float4*>(ws + L.hs);
-    a.accBC = reinterpret_cast<float*>(ws + L.accBC);
-    a.accA = reinterpret_cast<float*>(ws + L.accA);
-    a.accD = reinterpret_cast<float*>(ws + L.accD);
     a.d_x = d->d_x; a.d_dT = d->d_dT; a.d_dL = d->d_dL;
-    if (cudaMemsetAsync(ws + L.acc_begin, 0, L.total - L.acc_begin, st) != cudaSuccess) return M2D_ERR_LAUNCH;
+    const size_t npn = (size_t)d->B * d->H * d->W * d->N, en = (size_t)d->E * d->N;
+    if (d->dtype == M2D_F32) {
+        a.accBT = static_cast<float*>(d->d_BT); a.accBL = static_cast<float*>(d->d_BL); a.accC = static_cast<float*>(d->d_C);
+        a.accAT = static_cast<float*>(d->d_AT); a.accAL = static_cast<float*>(d->d_AL); a.accD = static_cast<float*>(d->d_D);
+        bool ok = cudaMemsetAsync(a.accBT, 0, npn * 4, st) == cudaSuccess && cudaMemsetAsync(a.accBL, 0, npn * 4, st) == cudaSuccess &&
+                  cudaMemsetAsync(a.accC, 0, npn * 4, st) == cudaSuccess && cudaMemsetAsync(a.accAT, 0, en * 4, st) == cudaSuccess &&
+                  cudaMemsetAsync(a.accAL, 0, en * 4, st) == cudaSuccess && cudaMemsetAsync(a.accD, 0, (size_t)d->E * 4, st) == cudaSuccess;
+        if (!ok) return M2D_ERR_LAUNCH;
+    } else {
+        float* acc = reinterpret_cast<float*>(ws + L.acc);
+        a.accBT = acc; a.accBL = acc + npn; a.accC = acc + 2 * npn;
+        a.accAT = acc + 3 * npn; a.accAL = a.accAT + en; a.accD = a.accAL + en;
+        if (cudaMemsetAsync(acc, 0, L.acc_bytes, st) != cudaSuccess) return M2D_ERR_LAUNCH;
+    }
     dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
     auto kern = vec ? m2d_bwd_kernel<io_t, true> : m2d_bwd_kernel<io_t, false>;
     if (pl.smem > 48 * 1024 &&
@@ -162,13 +171,15 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
         return M2D_ERR_LAUNCH;
     kern<<<grid, block, pl.smem, st>>>(a);
     if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
-    const long long npix = (long long)d->B * d->H * d->W;
-    const int fin_blocks = (int)((npix * d->N + 255) / 256 < 148 * 8 ? (npix * d->N + 255) / 256 : 148 * 8);
-    m2d_bwd_finalize<io_t><<<fin_blocks, 256, 0, st>>>(a.accBC, a.accA, a.accD, static_cast<io_t*>(d->d_BT),
-                                                      static_cast<io_t*>(d->d_BL), static_cast<io_t*>(d->d_C),
-                                                      static_cast<io_t*>(d->d_AT), static_cast<io_t*>(d->d_AL),
-                                                      static_cast<io_t*>(d->d_D), npix, d->N, d->E);
-    return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
+    if (d->dtype != M2D_F32) {
+        const int fin_blocks = (int)((npn + 255) / 256 < 148 * 8 ? (npn + 255) / 256 : 148 * 8);
+        m2d_bwd_finalize<io_t><<<fin_blocks, 256, 0, st>>>(a.accBT, static_cast<io_t*>(d->d_BT), static_cast<io_t*>(d->d_BL),
+                                                          static_cast<io_t*>(d->d_C), static_cast<io_t*>(d->d_AT),
+                                                          static_cast<io_t*>(d->d_AL), static_cast<io_t*>(d->d_D),
+                                                          (long long)npn, (long long)en, d->E);
+        if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
+    }
+    return M2D_OK;
 }
 
 }  // namespace m2d

@@ -67,14 +67,15 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
     float4* const harea = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes(nwarps)) + lane;
     float4* const h_own = harea + (r + 1) * kSlotPair;                        // this row's h[i][j-1]
     float4* const h_up = harea + r * kSlotPair;                               // the row above: h[i-1][j]
-    const float4* const hs_img = a.hs + ((size_t)b * groups + g) * H * W * kSlotF4 + lane;
+    constexpr int HB = HsBlock<io_t>::f4;   // float4 units per state-record block
+    const float4* const hs_img = a.hs + ((size_t)b * groups + g) * H * W * HB + lane;
     const bool y_lane = (g * kGroup + lane) < E;
     const bool ch_copier = (nq == 0) && (chv > 0);
     const bool st_copier = (cq == 0) && (nv > 0);
     const bool feeds_below = (r + 1 < Rb);     // a warp of this CTA owns the row below
     const bool hi16 = (cq & 4) != 0, hi8 = (cq & 2) != 0, hi4 = (cq & 1) != 0;
     const int db_n = n0 + (hi8 ? 2 : 0) + (hi4 ? 1 : 0);
-    const int db_off = (hi16 ? 16 : 0) + db_n;
+    float* const db_acc = hi16 ? a.accBL : a.accBT;
     const bool db_lane = db_n < a.N;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     const float ninf = __int_as_float(0xff800000);
@@ -95,12 +96,27 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
     st.phl = nullptr;
     st.cfac = st.mT = st.mL = st.offT = st.offL = 0.f;
 
+    // One state-record block, global -> shared (2 KiB of fp32 states or 1 KiB of bf16 states).
+    auto copy_block = [&](bool on, unsigned dst, const float4* src) {
+        if (sizeof(io_t) == 2) cp_async16x2_if(on, dst, src);
+        else cp_async16x4_if(on, dst, src);
+    };
+    // Four states of channel c of a staged block as floats.
+    auto block_states = [&](const float4* area, int c) -> float4 {
+        if (sizeof(io_t) == 2) {
+            const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(area + (c >> 1) * 32) + (c & 1) * 8);
+            return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                               __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+        }
+        return area[c * 32];
+    };
+
     // Fetch h[i][W-1] of the row this warp starts next, for the warp of the row below.
     auto prefetch_row_end = [&](int q, int par) {
         const int i = q * Rb + r;
         if (feeds_below && r < Rb && i < H) {
-            const float4* src = hs_img + ((size_t)i * W + (W - 1)) * kSlotF4;
-            cp_async16x4_if(true, smem_u32(h_own + par * kSlotF4), src);
+            const float4* src = hs_img + ((size_t)i * W + (W - 1)) * HB;
+            copy_block(true, smem_u32(h_own + par * kSlotF4), src);
         }
     };
 
@@ -113,7 +129,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
             st.pull_l = st.row_l && (rr == 0) && (i + 1 < H);      // pT of the row below comes through the ring
             st.top_l = st.row_l && (r == 0) && (i > 0);            // h of the row above is not in this band
             st.pixl = (b * H + i) * W + (W - 1);
-            st.phl = hs_img + ((size_t)i * W + (W - 2)) * kSlotF4;
+            st.phl = hs_img + ((size_t)i * W + (W - 2)) * HB;
         }
         const int j = W - 1 - st.jl;
         if (st.row_l) {
@@ -130,11 +146,11 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 stage4<VEC>(st_copier, stg + (36 + nq) * 16, static_cast<const io_t*>(a.BL), st.pixl * pBL + n0, nv);
                 stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), st.pixl * pC + n0, nv);
             }
-            cp_async16x4_if(j > 0, smem_u32(h_own + par * kSlotF4), st.phl);
-            cp_async16x4_if(st.top_l, smem_u32(h_up + par * kSlotF4), st.phl + (ptrdiff_t)(1 - W) * kSlotF4);
+            copy_block(j > 0, smem_u32(h_own + par * kSlotF4), st.phl);
+            copy_block(st.top_l, smem_u32(h_up + par * kSlotF4), st.phl + (ptrdiff_t)(1 - W) * HB);
             cp_async16x4_if(st.pull_l, smem_u32(my + par * kSlotF4), ring + j * kSlotF4);
             --st.pixl;
-            st.phl -= kSlotF4;
+            st.phl -= HB;
         }
         // last cell of a row: its own h[i][-1] does not exist (that gate is zero), so the slot is
         // free for the right-most block of the row this warp starts next
@@ -193,8 +209,8 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
             float o_dT[4], o_dL[4], o_dx[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const float4 hl4 = h_own[(par ^ 1) * kSlotF4 + c * 32];
-                const float4 ht4 = h_up[(par ^ 1) * kSlotF4 + c * 32];
+                const float4 hl4 = block_states(h_own + (par ^ 1) * kSlotF4, c);
+                const float4 ht4 = block_states(h_up + (par ^ 1) * kSlotF4, c);
                 const float4 pd4 = st.bottom_c ? zero4 : my[(par ^ 1) * kSlotF4 + c * 32];
                 const float hls[4] = {hl4.x, hl4.y, hl4.z, hl4.w};
                 const float hts[4] = {ht4.x, ht4.y, ht4.z, ht4.w};
@@ -272,7 +288,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 float v = hi4 ? m1 : m0;
                 v += __shfl_xor_sync(0xffffffffu, hi4 ? m0 : m1, 4);
                 // this lane now owns array (hi16 ? d_BL : d_BT), state n0 + 2*hi8 + hi4
-                if (db_lane) atomicAdd(a.accBC + ((long long)st.pixc * 48 + db_off), v);
+                if (db_lane) atomicAdd(db_acc + ((long long)st.pixc * a.N + db_n), v);
             }
             --st.pixc;
         }

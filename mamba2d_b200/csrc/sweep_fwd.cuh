@@ -35,10 +35,13 @@ struct ScanArgs {
     int Rb, nbands;
     // ---- backward only ----
     const void* gy;
-    float4* hs;               // full state record: [b][group][H*W][4][32] float4
-    float* accBC;             // fp32 accumulators [B*H*W][48]: d_BT | d_BL | d_C
-    float* accA;              // fp32 accumulators [2][E][N]:   d_AT | d_AL
-    float* accD;              // fp32 accumulators [E]
+    float4* hs;               // full state record: [b][group][H*W] blocks; a block is [4][32] float4 (fp32 I/O)
+                              // or [2][32] uint4 holding 16 bf16 states per lane (bf16 I/O)
+    // fp32 accumulators of the reduced gradients, zeroed before the kernel.  For fp32 I/O they are
+    // the caller's gradient tensors themselves; for bf16 I/O they live in the workspace.
+    float *accBT, *accBL, *accC;   // [B*H*W][N]
+    float *accAT, *accAL;          // [E][N]
+    float* accD;                   // [E]
     void *d_x, *d_dT, *d_dL;
 };
 typedef ScanArgs FwdArgs;
@@ -47,6 +50,9 @@ typedef ScanArgs FwdArgs;
 // and writes slot k+1; slot 0 receives the ring pull.
 constexpr int kSlotPair = 2 * kSlotF4;
 __host__ __device__ inline size_t handoff_bytes(int warps) { return (size_t)(warps + 1) * kSlotPair * sizeof(float4); }
+// float4 units of one (cell, warp) block of the state record
+template <typename io_t> struct HsBlock { static constexpr int f4 = sizeof(io_t) == 2 ? 64 : 128; };
+
 // Dynamic shared memory of a sweep: the hand-off slots followed by one input stage per warp.
 __host__ __device__ inline size_t sweep_smem_bytes(int warps) { return handoff_bytes(warps) + (size_t)warps * 2 * kStageBytes; }
 // The per-(channel,state) parameters A*log2(e) of the CTA's 32 channels live in shared memory
@@ -184,7 +190,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
             st.row0_c = (i == 0);
             st.push_c = st.row_c && (r == Rb - 1) && (st.qc < nbands - 1);
             st.pixc = (b * H + i) * W;
-            if (STORE_HS) st.phs = a.hs + (((size_t)b * groups + g) * H * W + (size_t)i * W) * kSlotF4 + lane;
+            if (STORE_HS) st.phs = a.hs + (((size_t)b * groups + g) * H * W + (size_t)i * W) * HsBlock<io_t>::f4 + lane;
         }
         if (st.row_c) {
             const bool first = (st.jc == 0);
@@ -256,7 +262,17 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                 float4* dst = my + kSlotPair + par * kSlotF4;
                 dst[0] = h0; dst[32] = h1; dst[64] = h2; dst[96] = h3;
                 stcg4_if(st.push_c, ring + st.jc * kSlotF4, h0, h1, h2, h3);
-                if (STORE_HS) stcg4_if(true, st.phs, h0, h1, h2, h3);
+                if (STORE_HS) {
+                    if (sizeof(io_t) == 2) {
+                        // bf16 I/O: the record holds bf16 states (the gradients that use it are bf16 anyway)
+                        __stcg(st.phs, make_float4(__uint_as_float(pack_bf16x2(h0.x, h0.y)), __uint_as_float(pack_bf16x2(h0.z, h0.w)),
+                                                   __uint_as_float(pack_bf16x2(h1.x, h1.y)), __uint_as_float(pack_bf16x2(h1.z, h1.w))));
+                        __stcg(st.phs + 32, make_float4(__uint_as_float(pack_bf16x2(h2.x, h2.y)), __uint_as_float(pack_bf16x2(h2.z, h2.w)),
+                                                        __uint_as_float(pack_bf16x2(h3.x, h3.y)), __uint_as_float(pack_bf16x2(h3.z, h3.w))));
+                    } else {
+                        stcg4_if(true, st.phs, h0, h1, h2, h3);
+                    }
+                }
             }
 
             if (STORE_HS) {
@@ -268,8 +284,8 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                 float k = hi8 ? k1 : k0;
                 k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
                 k += __shfl_xor_sync(0xffffffffu, k, 4);
-                if (dc_lane) atomicAdd(a.accBC + ((long long)st.pixc * 48 + 32 + dc_n), k);
-                st.phs += kSlotF4;
+                if (dc_lane) atomicAdd(a.accC + ((long long)st.pixc * a.N + dc_n), k);
+                st.phs += HsBlock<io_t>::f4;
             } else {
                 const float ysum = reduce_states(yacc[0], yacc[1], yacc[2], yacc[3], nq);
                 if (y_lane) store1(static_cast<io_t*>(a.y), st.pixc * E + g * kGroup + lane, fmaf(sel4(cur.x, nq), D_own, ysum));
