@@ -236,7 +236,8 @@ struct Plan {
     int warps;         // row-warps per CTA
     int Rb;            // rows per band (<= warps)
     int nbands;        // ceil(H / Rb)
-    int grid_x;        // CTAs per channel group; each walks images blockIdx.x, +grid_x, ...
+    int grid_x;        // image chains per channel group; chain k walks images k, k + grid_x, ...
+    int chain;         // CTAs per chain (forward only; > 1 when there are far fewer images than SMs)
     size_t smem;       // dynamic shared memory per CTA
     size_t scratch;    // workspace bytes
 };

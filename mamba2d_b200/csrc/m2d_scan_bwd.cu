@@ -147,6 +147,7 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     a.y = nullptr;
     a.ring = reinterpret_cast<float4*>(ws + L.ring);
     a.Rb = pl.Rb; a.nbands = pl.nbands;
+    a.chain = 1; a.bnd = nullptr; a.progress = nullptr; a.status = nullptr;
     a.gy = d->gy;
     a.hs = reinterpret_cast<float4*>(ws + L.hs);
     a.d_x = d->d_x; a.d_dT = d->d_dT; a.d_dL = d->d_dL;

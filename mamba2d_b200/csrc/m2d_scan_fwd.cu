@@ -4,7 +4,7 @@
 
 namespace m2d {
 
-template <typename io_t, bool VEC>
+template <typename io_t, bool VEC, bool CHAINED>
 __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
     extern __shared__ float4 handoff[];
     const int lane = threadIdx.x & 31;
@@ -24,8 +24,11 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
     if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane);
     __syncthreads();
 
-    const int nb = (a.B - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    forward_sweep<io_t, VEC, false>(a, handoff, params, D_own, blockIdx.x, gridDim.x, nb);
+    // gridDim.x = chains x a.chain: CTA (chain_id, cpos) walks images chain_id, chain_id + chains, ...
+    const int chains = (int)gridDim.x / a.chain;
+    const int chain_id = (int)blockIdx.x / a.chain, cpos = (int)blockIdx.x % a.chain;
+    const int nb = (a.B - chain_id + chains - 1) / chains;
+    forward_sweep<io_t, VEC, false, CHAINED>(a, handoff, params, D_own, chain_id, chains, nb, cpos, a.chain);
 }
 
 template <typename io_t>
@@ -36,11 +39,25 @@ static int launch_fwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     a.BT = d->BT; a.BL = d->BL; a.C = d->C; a.D = d->D;
     a.pBT = d->BT_pitch; a.pBL = d->BL_pitch; a.pC = d->C_pitch;
     a.y = d->y;
+    a.gy = nullptr;
     a.ring = static_cast<float4*>(d->workspace);
     a.hs = nullptr;
     a.Rb = pl.Rb; a.nbands = pl.nbands;
-    dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
-    auto kern = vec ? m2d_fwd_kernel<io_t, true> : m2d_fwd_kernel<io_t, false>;
+    a.chain = pl.chain;
+    a.bnd = nullptr; a.progress = nullptr; a.status = nullptr;
+    if (pl.chain > 1) {
+        // workspace = [boundary rows of every band][column counters + status word]
+        char* ws = static_cast<char*>(d->workspace);
+        const size_t nband = (size_t)d->B * pl.groups * pl.nbands;
+        const size_t bnd_bytes = align256(nband * d->W * kSlotF4 * sizeof(float4));
+        a.bnd = reinterpret_cast<float4*>(ws);
+        a.progress = reinterpret_cast<int*>(ws + bnd_bytes);
+        a.status = a.progress + nband;
+        if (cudaMemsetAsync(a.progress, 0, (nband + 1) * sizeof(int), st) != cudaSuccess) return M2D_ERR_LAUNCH;
+    }
+    dim3 grid(pl.grid_x * pl.chain, pl.groups), block(pl.warps * 32);
+    auto kern = pl.chain > 1 ? (vec ? m2d_fwd_kernel<io_t, true, true> : m2d_fwd_kernel<io_t, false, true>)
+                             : (vec ? m2d_fwd_kernel<io_t, true, false> : m2d_fwd_kernel<io_t, false, false>);
     if (pl.smem > 48 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
         return M2D_ERR_LAUNCH;

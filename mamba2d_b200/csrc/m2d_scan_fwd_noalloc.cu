@@ -84,6 +84,7 @@ static int launch_noalloc(const m2d_scan_desc* d, const Plan& pl, bool vec, floa
     a.y = d->y;
     a.ring = ring;
     a.Rb = pl.Rb; a.nbands = pl.nbands;
+    a.chain = 1;
     dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
     auto kern = vec ? m2d_fwd_noalloc_kernel<io_t, true> : m2d_fwd_noalloc_kernel<io_t, false>;
     if (pl.smem > 48 * 1024 &&
@@ -99,7 +100,7 @@ extern "C" int m2d_scan_fwd_noalloc(const m2d_scan_desc* d, void* stream) {
     int rc = m2d::check_desc(d, false, true);
     if (rc != M2D_OK) return rc;
     if (!d->y) return M2D_ERR_NULL;
-    const m2d::Plan pl = m2d::plan_fwd(d);
+    const m2d::Plan pl = m2d::plan_fwd(d, false);   // one CTA per image: the fixed array holds per-CTA rings only
     if (pl.scratch > M2D_NOALLOC_SCRATCH_BYTES) return M2D_ERR_TOO_LARGE;   // decided before any device work
     float4* ring = nullptr;
     rc = m2d::ring_address(&ring);

@@ -87,14 +87,29 @@ inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int warps_per_sm)
     p.grid_x = (int)((d->B + per - 1) / per);
     p.smem = ((size_t)2 * (p.warps + 1) * kSlotF4 + (size_t)p.warps * 2 * kStageSlots + 256) * sizeof(float4);   // + parameters
     p.scratch = 0;
+    p.chain = 1;
     return p;
 }
 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
-inline Plan plan_fwd(const m2d_scan_desc* d) {
+inline Plan plan_fwd(const m2d_scan_desc* d, bool allow_chain = true) {
     Plan p = plan_common(d, 8, 16);
-    if (p.nbands > 1) p.scratch = align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
+    // Few images on a large map: give every image a chain of CTAs, each owning every chain-th band,
+    // so that the bands of one image run as a pipeline across SMs.  All CTAs must be resident.
+    const long long slots = (long long)(16 / p.warps > 0 ? 16 / p.warps : 1) * sm_count();
+    const long long ctas = (long long)p.grid_x * p.groups;
+    if (allow_chain && p.nbands > 1 && ctas * 2 <= slots) {
+        long long c = slots / ctas;
+        if (c > p.nbands) c = p.nbands;
+        p.chain = (int)c;
+    }
+    if (p.chain > 1) {
+        const size_t nband = (size_t)d->B * p.groups * p.nbands;
+        p.scratch = align256(nband * d->W * kSlotF4 * sizeof(float4)) + align256((nband + 1) * sizeof(int));
+    } else if (p.nbands > 1) {
+        p.scratch = align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
+    }
     return p;
 }
 

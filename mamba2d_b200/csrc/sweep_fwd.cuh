@@ -33,6 +33,13 @@ struct ScanArgs {
     void* y;
     float4* ring;             // per-CTA band-boundary ring: [cta][W][4][32] float4
     int Rb, nbands;
+    // ---- several CTAs per image (large maps, few images): CTA c of a chain of `chain` CTAs owns the
+    // bands q = c, c + chain, ... of its images; the last row of band q reaches band q+1 (another
+    // CTA) through `bnd` and the per-band column counter `progress`
+    int chain;                // 1 = one CTA per image
+    float4* bnd;              // [image][group][band][W][4][32] float4
+    int* progress;            // [image][group][band]: columns of the band's last row published so far
+    int* status;              // nonzero if a wait on `progress` gave up (results are then invalid)
     // ---- backward only ----
     const void* gy;
     float4* hs;               // full state record: [b][group][H*W] blocks; a block is [4][32] float4 (fp32 I/O)
@@ -90,6 +97,30 @@ __device__ __forceinline__ void load_param_block(float (&dst)[4][4], const void*
             dst[c][n] = (c < chv && n < nv) ? load1(static_cast<const io_t*>(P), (long long)(ch0 + c) * N + n0 + n) * scale : 0.f;
 }
 
+// Bounded wait of a consumer warp on a producer's column counter (another CTA).  Returns the value
+// seen; after kWaitPolls unsuccessful polls it records the failure in *status and gives up, so a
+// kernel can never spin forever.
+constexpr int kWaitPolls = 1 << 22;
+__device__ __forceinline__ int wait_columns(const int* counter, int need, int* status, int lane) {
+    int seen = 0;
+    if (lane == 0) {
+        const volatile int* c = counter;
+        int polls = 0;
+        seen = *c;
+        while (seen < need) {
+            if (++polls > kWaitPolls || *reinterpret_cast<volatile int*>(status) != 0) {
+                atomicExch(status, 1);
+                seen = 0x7fffffff;   // stop waiting for the rest of the kernel
+                break;
+            }
+            __nanosleep(64);
+            seen = *c;
+        }
+        __threadfence();   // order the data reads after the counter read
+    }
+    return __shfl_sync(0xffffffffu, seen, 0);
+}
+
 // Per-warp running state of a forward sweep.  Addresses are rebuilt every step from a running 32-bit
 // pixel index (one multiply-add each); the host guarantees that every element index fits 31 bits.
 struct FwdRun {
@@ -97,19 +128,25 @@ struct FwdRun {
     int pixl;               // flat pixel index (b*H + i)*W + j
     int jl, ql, bil;
     bool row_l, pull_l;
+    int seen;               // columns of the band above known to be published (chained CTAs)
+    const float4* pull;     // boundary row of the band above
+    const int* pcount;      // its column counter
     // ---- compute side: the cell whose arithmetic runs now ----
     int pixc;
     float4* phs;            // state record of the current cell (recompute sweep only)
     int jc, qc, bic;
     bool row_c, row0_c, push_c;
+    float4* push;           // where this band's last row goes
+    int* ccount;            // its column counter (chained CTAs)
 };
 
 // One CTA's forward sweep over images img0, img0 + img_stride, ... (nb of them).  `handoff` is
 // shared memory of handoff_bytes(warps), zero-initialised by the caller.  With STORE_HS every fresh
 // state block is also written to a.hs and d_C is accumulated (backward's recompute sweep).
-template <typename io_t, bool VEC, bool STORE_HS>
+template <typename io_t, bool VEC, bool STORE_HS, bool CHAINED = false>
 __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff, const float4* params,
-                                              float D_own, int img0, int img_stride, int nb) {
+                                              float D_own, int img0, int img_stride, int nb, int cpos = 0, int chain_arg = 1) {
+    const int chain = CHAINED ? chain_arg : 1;   // compile-time 1 in the batch kernels
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
     const int g = blockIdx.y, groups = gridDim.y;
@@ -117,7 +154,8 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
     const int W = a.W, H = a.H, E = a.E, Rb = a.Rb, nbands = a.nbands;
-    const int T = nb * nbands * W;            // cells in this warp's sequence
+    const int nq_c = chain > 1 ? (nbands - cpos + chain - 1) / chain : nbands;   // bands of an image this CTA owns
+    const int T = nb * nq_c * W;              // cells in this warp's sequence
     const int steps = T + Rb - 1;
     const int pBT = (int)a.pBT, pBL = (int)a.pBL, pC = (int)a.pC;
     float4* const ring = a.ring + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * W) * kSlotF4 + lane;
@@ -146,16 +184,26 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
     st.row_l = st.pull_l = st.row_c = st.row0_c = st.push_c = false;
     st.pixl = st.pixc = 0;
     st.phs = nullptr;
+    st.seen = 0; st.pull = ring; st.pcount = nullptr; st.push = ring; st.ccount = nullptr;
 
     // ---- issue the loads of the next cell of this warp's sequence into `nxt` -------------------
     auto load_phase = [&](int par) {
         if (st.jl == 0) {   // start of a row
-            const int i = st.ql * Rb + r;
+            const int q = cpos + st.ql * chain;
+            const int i = q * Rb + r;
             const int b = img0 + st.bil * img_stride;
             st.row_l = (r < Rb) && (i < H);
-            st.pull_l = st.row_l && (r == 0) && (st.ql > 0);
+            st.pull_l = st.row_l && (r == 0) && (q > 0);
             st.pixl = (b * H + i) * W;
+            if (chain > 1 && q > 0) {   // the band above belongs to another CTA
+                const size_t band = ((size_t)b * groups + g) * nbands + (q - 1);
+                st.pull = a.bnd + band * W * kSlotF4 + lane;
+                st.pcount = a.progress + band;
+                st.seen = 0;
+            }
         }
+        if (chain > 1 && st.pull_l && st.seen <= st.jl)
+            st.seen = wait_columns(st.pcount, st.jl + 1, a.status, lane);
         if (st.row_l) {
             char* stg = stage + par * kStageBytes;
             if (VEC) {
@@ -172,23 +220,29 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                 stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), st.pixl * pC + n0, nv);
             }
             // the row above lives in the previous band: pull it from the ring into slot 0
-            cp_async16x4_if(st.pull_l, smem_u32(my + par * kSlotF4), ring + st.jl * kSlotF4);
+            cp_async16x4_if(st.pull_l, smem_u32(my + par * kSlotF4), st.pull + st.jl * kSlotF4);
             ++st.pixl;
         }
         if (++st.jl == W) {
             st.jl = 0;
-            if (++st.ql == nbands) { st.ql = 0; ++st.bil; }
+            if (++st.ql == nq_c) { st.ql = 0; ++st.bil; }
         }
     };
 
     // ---- arithmetic of the current cell from `cur`; reads hand-off parity par^1, writes par ----
     auto compute_phase = [&](int par) {
         if (st.jc == 0) {
-            const int i = st.qc * Rb + r;
+            const int q = cpos + st.qc * chain;
+            const int i = q * Rb + r;
             const int b = img0 + st.bic * img_stride;
             st.row_c = (r < Rb) && (i < H);
             st.row0_c = (i == 0);
-            st.push_c = st.row_c && (r == Rb - 1) && (st.qc < nbands - 1);
+            st.push_c = st.row_c && (r == Rb - 1) && (q < nbands - 1);
+            if (chain > 1) {
+                const size_t band = ((size_t)b * groups + g) * nbands + q;
+                st.push = a.bnd + band * W * kSlotF4 + lane;
+                st.ccount = a.progress + band;
+            }
             st.pixc = (b * H + i) * W;
             if (STORE_HS) st.phs = a.hs + (((size_t)b * groups + g) * H * W + (size_t)i * W) * HsBlock<io_t>::f4 + lane;
         }
@@ -261,7 +315,13 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                 const float4 h2 = make_float4(h[2][0], h[2][1], h[2][2], h[2][3]), h3 = make_float4(h[3][0], h[3][1], h[3][2], h[3][3]);
                 float4* dst = my + kSlotPair + par * kSlotF4;
                 dst[0] = h0; dst[32] = h1; dst[64] = h2; dst[96] = h3;
-                stcg4_if(st.push_c, ring + st.jc * kSlotF4, h0, h1, h2, h3);
+                stcg4_if(st.push_c, st.push + st.jc * kSlotF4, h0, h1, h2, h3);
+                if (chain > 1 && st.push_c) {
+                    // publish the column: data first, then the counter
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) *reinterpret_cast<volatile int*>(st.ccount) = st.jc + 1;
+                }
                 if (STORE_HS) {
                     if (sizeof(io_t) == 2) {
                         // bf16 I/O: the record holds bf16 states (the gradients that use it are bf16 anyway)
@@ -294,7 +354,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
         }
         if (++st.jc == W) {
             st.jc = 0;
-            if (++st.qc == nbands) { st.qc = 0; ++st.bic; }
+            if (++st.qc == nq_c) { st.qc = 0; ++st.bic; }
         }
     };
 

@@ -56,6 +56,8 @@ FWD_SHAPES = [
     (1, 13, 3, 32, 16),     # narrow map: band height limited by W
     (5, 3, 19, 32, 8),
     (1, 64, 64, 32, 16),
+    (1, 200, 136, 64, 16),  # large map, one image: many CTAs chained along the bands of the image
+    (2, 96, 40, 32, 16),
 ]
 
 
