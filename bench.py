@@ -270,7 +270,7 @@ def run_ours(args):
         "e2e": {"value": el * world * e2e_steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                 "note": "pinned host inputs -> device, fwd+bwd through the public API, y and all nine gradients -> pinned host"},
-        "gpu_launches": args.steps * len(STAGES) * 3,   # per shape: forward kernel, backward kernel, cast kernel
+        "gpu_launches": args.steps * len(STAGES) * (2 if args.dtype == "f32" else 3),   # per shape: forward kernel, backward kernel (+ cast kernel for bf16)
         "roofline": {"bound": "hbm", "kernel": "m2d_bwd_kernel @ D=64,H=W=56,B=128", "achieved": dom_bytes / dom["bwd_ms"] / 1e6,
                      "peak": peak, "unit": "GB/s", "frac": dom_bytes / dom["bwd_ms"] / 1e6 / peak,
                      "peak_kind": peak_kind, "algorithmic_bytes": dom_bytes, "ms": dom["bwd_ms"],
@@ -284,6 +284,8 @@ def run_ours(args):
         out["cpu_baseline"] = cpu_baseline(args.dtype)
     if world == 1 and not args.no_ref_gpu:
         out["reference_gpu"] = reference_gpu(devin, args.dtype)
+    if world == 1:
+        out["m2dt_scan_layers"] = m2dt_scan_layers(dev)
     print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -314,6 +316,40 @@ def cpu_baseline(dtype, sample_batch=64, repeat=1, threads=None):
             "sample": f"fwd+bwd of the four stage shapes at batch {sample_batch} (of 128), fp32 arithmetic, "
                       f"{repeat} pass(es), {t:.1f} s wall on {cores} threads",
             "seconds": t}
+
+
+def m2dt_scan_layers(dev, batch=128, iters=5):
+    """The scan layers of one M2D-T forward as the backbone calls them: wavefront_scan_cuda(x, weights)
+    in bf16 under inference mode, projections included, 3 blocks at (D=64, 56x56) + 3 blocks at
+    (D=128, 28x28) -- the only stages of the shipped M2D-T config that use the scan (stages 3-4 are
+    attention).  Images/s of this part alone; the rest of the backbone is outside this repository."""
+    import torch
+    from mamba2d_b200 import wavefront_scan_cuda
+    from oracle import inputs as oin
+    names = ("AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w", "dt_projL_b", "D")
+    layers = []
+    for D, HW, blocks in ((64, 56, 3), (128, 28, 3)):
+        g = torch.Generator().manual_seed(D)
+        x = torch.randn(batch, HW, HW, D, generator=g).to(dev, torch.bfloat16)
+        for k in range(blocks):
+            w = oin.make_module_params(D, NSTATE, seed=10 * D + k)
+            layers.append((x, [w[n].to(dev) for n in names]))
+    def run():
+        with torch.inference_mode():
+            for x, ws in layers:
+                wavefront_scan_cuda(x, *ws)
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    return {"images_per_s": batch / (ms * 1e-3), "ms": ms, "batch": batch, "dtype": "bf16",
+            "what": "6 scan layers of M2D-T (3x D=64@56x56, 3x D=128@28x28) through wavefront_scan_cuda incl. projections"}
 
 
 def reference_gpu(devin, dtype, iters=2):

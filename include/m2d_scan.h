@@ -105,6 +105,16 @@ uint64_t m2d_scan_bwd_workspace(const m2d_scan_desc *desc);
 int m2d_scan_fwd(const m2d_scan_desc *desc, void *stream);
 
 /*
+ * Large maps with few images run several CTAs per image that wait on one another with bounded
+ * polling.  If such a wait ever gives up (it cannot when the kernel has the GPU to itself), the
+ * kernel still terminates and writes a nonzero int32 status word into the workspace.  This returns
+ * the byte offset of that word inside the workspace for this problem, or -1 if the problem does
+ * not use cross-CTA waits.  Read the word after synchronising the stream.  No counterpart in the
+ * reference (its launches are serialised by the host).
+ */
+int64_t m2d_scan_fwd_status_offset(const m2d_scan_desc *desc);
+
+/*
  * Backward with recomputation of the hidden state: all nine gradients of the forward.
  * Replaces the body of wf_cuda_fn_pr.backward (wavefront_cuda.py:163-196): the recompute of hs,
  * wf_bwd (wf_cuda_bind.cpp:36-47) and fused_backward_math (wavefront_cuda.py:97-139).

@@ -72,6 +72,14 @@ extern "C" uint64_t m2d_scan_fwd_workspace(const m2d_scan_desc* d) {
     return m2d::plan_fwd(d).scratch;
 }
 
+extern "C" int64_t m2d_scan_fwd_status_offset(const m2d_scan_desc* d) {
+    if (m2d::check_desc(d, false, false) != M2D_OK) return -1;
+    const m2d::Plan pl = m2d::plan_fwd(d);
+    if (pl.chain <= 1) return -1;
+    const size_t nband = (size_t)d->B * pl.groups * pl.nbands;
+    return (int64_t)(m2d::align256(nband * d->W * m2d::kSlotF4 * sizeof(float4)) + nband * sizeof(int));
+}
+
 extern "C" int m2d_scan_fwd(const m2d_scan_desc* d, void* stream) {
     int rc = m2d::check_desc(d, false, true);
     if (rc != M2D_OK) return rc;

@@ -16,6 +16,7 @@ There is no PyTorch or CPU fallback: tensors must live on a CUDA device and the 
 must be present, otherwise a ``RuntimeError`` is raised.
 """
 import ctypes
+import os
 
 import torch
 import torch.library
@@ -26,6 +27,7 @@ from . import _lib
 __all__ = ["wavefront_scan_cuda", "wf_cuda_fn_pr", "wf_cuda_fn_fr", "proj_params", "scan_fwd", "scan_bwd"]
 
 _DTYPES = {torch.float32: _lib.M2D_F32, torch.bfloat16: _lib.M2D_BF16}
+_CHECK_STATUS = os.environ.get("M2D_CHECK_STATUS", "0") == "1"
 
 
 # -----------------------------------------------------------------------------
@@ -99,7 +101,11 @@ def _workspace(d, nbytes, device, keep):
 
 
 def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D):
-    """Fused forward: y (B,H,W,E) in ``x.dtype``.  Inputs as ``wf_cuda_fn_pr.apply`` takes them."""
+    """Fused forward: y (B,H,W,E) in ``x.dtype``.  Inputs as ``wf_cuda_fn_pr.apply`` takes them.
+
+    With few images on a large map the kernel runs several CTAs per image that wait on one another
+    with bounded polling; set ``M2D_CHECK_STATUS=1`` to synchronise after the call and raise if
+    such a wait ever gave up (status word in the workspace, see m2d_scan_fwd_status_offset)."""
     _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
     L = _lib.lib()
     with torch.cuda.device(x.device):
@@ -109,6 +115,10 @@ def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D):
         _workspace(d, L.m2d_scan_fwd_workspace(ctypes.byref(d)), x.device, keep)
         rc = L.m2d_scan_fwd(ctypes.byref(d), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     _lib.check(rc, "m2d_scan_fwd")
+    if _CHECK_STATUS:
+        off = L.m2d_scan_fwd_status_offset(ctypes.byref(d))
+        if off >= 0 and keep[-1][off:off + 4].view(torch.int32).item() != 0:      # .item() synchronises
+            raise RuntimeError("m2d_scan_fwd: a wait between CTAs of one image timed out; the output is invalid")
     return y
 
 

@@ -76,6 +76,13 @@ def test_workspace_queries(L):
     assert L.m2d_scan_fwd_workspace(ctypes.byref(_desc(H=1))) == 0    # invalid descriptor
 
 
+def test_status_offset_only_for_chained_problems(L):
+    assert L.m2d_scan_fwd_status_offset(ctypes.byref(_desc(B=128, H=56, W=56))) == -1      # enough images: one CTA each
+    d = _desc(B=1, H=256, W=256)
+    off = L.m2d_scan_fwd_status_offset(ctypes.byref(d))
+    assert 0 < off < L.m2d_scan_fwd_workspace(ctypes.byref(d)) and off % 4 == 0
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "_LIB", None)
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
