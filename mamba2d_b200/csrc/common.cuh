@@ -237,6 +237,7 @@ struct Plan {
     int Rb;            // rows per band (<= warps)
     int nbands;        // ceil(H / Rb)
     int grid_x;        // image chains per channel group; chain k walks images k, k + grid_x, ...
+    int cb;            // cells per step and warp (forward only)
     int chain;         // CTAs per chain (forward only; > 1 when there are far fewer images than SMs)
     size_t smem;       // dynamic shared memory per CTA
     size_t scratch;    // workspace bytes

@@ -4,7 +4,7 @@
 
 namespace m2d {
 
-template <typename io_t, bool VEC, bool CHAINED>
+template <typename io_t, bool VEC, bool CHAINED, int CB>
 __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
     extern __shared__ float4 handoff[];
     const int lane = threadIdx.x & 31;
@@ -14,13 +14,13 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
 
-    const int total = (int)(sweep_smem_bytes(blockDim.x >> 5) / sizeof(float4));
+    const int total = (int)(sweep_smem_bytes(blockDim.x >> 5, CB) / sizeof(float4));
     for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 
     const int ch_own = g * kGroup + lane;
     const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
     __syncthreads();
-    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes((blockDim.x >> 5)));
+    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes((blockDim.x >> 5), CB));
     if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane);
     __syncthreads();
 
@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
     const int chains = (int)gridDim.x / a.chain;
     const int chain_id = (int)blockIdx.x / a.chain, cpos = (int)blockIdx.x % a.chain;
     const int nb = (a.B - chain_id + chains - 1) / chains;
-    forward_sweep<io_t, VEC, false, CHAINED>(a, handoff, params, D_own, chain_id, chains, nb, cpos, a.chain);
+    forward_sweep<io_t, VEC, false, CHAINED, CB>(a, handoff, params, D_own, chain_id, chains, nb, cpos, a.chain);
 }
 
 template <typename io_t>
@@ -55,12 +55,39 @@ static int launch_fwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
         a.status = a.progress + nband;
         if (cudaMemsetAsync(a.progress, 0, (nband + 1) * sizeof(int), st) != cudaSuccess) return M2D_ERR_LAUNCH;
     }
-    dim3 grid(pl.grid_x * pl.chain, pl.groups), block(pl.warps * 32);
-    auto kern = pl.chain > 1 ? (vec ? m2d_fwd_kernel<io_t, true, true> : m2d_fwd_kernel<io_t, false, true>)
-                             : (vec ? m2d_fwd_kernel<io_t, true, false> : m2d_fwd_kernel<io_t, false, false>);
+    dim3 block(pl.warps * 32);
+    void (*kern)(const FwdArgs);
+    if (pl.cb == 2) {
+        kern = pl.chain > 1 ? (vec ? m2d_fwd_kernel<io_t, true, true, 2> : m2d_fwd_kernel<io_t, false, true, 2>)
+                            : (vec ? m2d_fwd_kernel<io_t, true, false, 2> : m2d_fwd_kernel<io_t, false, false, 2>);
+    } else {
+        kern = pl.chain > 1 ? (vec ? m2d_fwd_kernel<io_t, true, true, 1> : m2d_fwd_kernel<io_t, false, true, 1>)
+                            : (vec ? m2d_fwd_kernel<io_t, true, false, 1> : m2d_fwd_kernel<io_t, false, false, 1>);
+    }
     if (pl.smem > 48 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
         return M2D_ERR_LAUNCH;
+    if (a.chain > 1) {
+        // CTAs of a chain wait on one another, so every CTA of the launch must be resident at the same
+        // time.  A cooperative launch guarantees that or fails cleanly; the chain is shortened until
+        // the device accepts it (the workspace layout does not depend on the chain length).
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)block.x, pl.smem) != cudaSuccess || per_sm < 1)
+            return M2D_ERR_LAUNCH;
+        const long long fit = (long long)per_sm * sm_count() / ((long long)pl.grid_x * pl.groups);
+        if (fit < a.chain) a.chain = fit < 1 ? 1 : (int)fit;
+        for (;;) {
+            dim3 grid(pl.grid_x * a.chain, pl.groups);
+            void* args[] = {&a};
+            const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), grid, block, args, pl.smem, st);
+            if (e == cudaSuccess) return M2D_OK;
+            cudaGetLastError();
+            if (e != cudaErrorCooperativeLaunchTooLarge || a.chain == 1) return M2D_ERR_LAUNCH;
+            a.chain = a.chain > 2 ? a.chain - a.chain / 4 - 1 : 1;
+        }
+    }
+    dim3 grid(pl.grid_x, pl.groups);
     kern<<<grid, block, pl.smem, st>>>(a);
     return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
 }

@@ -100,7 +100,7 @@ extern "C" int m2d_scan_fwd_noalloc(const m2d_scan_desc* d, void* stream) {
     int rc = m2d::check_desc(d, false, true);
     if (rc != M2D_OK) return rc;
     if (!d->y) return M2D_ERR_NULL;
-    const m2d::Plan pl = m2d::plan_fwd(d, false);   // one CTA per image: the fixed array holds per-CTA rings only
+    const m2d::Plan pl = m2d::plan_fwd(d, false, false);   // one CTA per image: the fixed array holds per-CTA rings only
     if (pl.scratch > M2D_NOALLOC_SCRATCH_BYTES) return M2D_ERR_TOO_LARGE;   // decided before any device work
     float4* ring = nullptr;
     rc = m2d::ring_address(&ring);

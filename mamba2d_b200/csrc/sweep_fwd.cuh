@@ -56,12 +56,12 @@ typedef ScanArgs FwdArgs;
 // Shared-memory hand-off layout: [slot 0..warps][parity 0..1][4][32] float4.  Rank k reads slot k
 // and writes slot k+1; slot 0 receives the ring pull.
 constexpr int kSlotPair = 2 * kSlotF4;
-__host__ __device__ inline size_t handoff_bytes(int warps) { return (size_t)(warps + 1) * kSlotPair * sizeof(float4); }
+__host__ __device__ inline size_t handoff_bytes(int warps, int cb = 1) { return (size_t)(warps + 1) * cb * kSlotPair * sizeof(float4); }
 // float4 units of one (cell, warp) block of the state record
 template <typename io_t> struct HsBlock { static constexpr int f4 = sizeof(io_t) == 2 ? 64 : 128; };
 
 // Dynamic shared memory of a sweep: the hand-off slots followed by one input stage per warp.
-__host__ __device__ inline size_t sweep_smem_bytes(int warps) { return handoff_bytes(warps) + (size_t)warps * 2 * kStageBytes; }
+__host__ __device__ inline size_t sweep_smem_bytes(int warps, int cb = 1) { return handoff_bytes(warps, cb) + (size_t)warps * 2 * cb * kStageBytes; }
 // The per-(channel,state) parameters A*log2(e) of the CTA's 32 channels live in shared memory
 // behind everything else: [AT | AL][4 channels][32 lanes] float4 (4 KiB), read block by block.
 constexpr int kParamF4 = 2 * 4 * 32;
@@ -141,12 +141,16 @@ struct FwdRun {
 };
 
 // One CTA's forward sweep over images img0, img0 + img_stride, ... (nb of them).  `handoff` is
-// shared memory of handoff_bytes(warps), zero-initialised by the caller.  With STORE_HS every fresh
-// state block is also written to a.hs and d_C is accumulated (backward's recompute sweep).
-template <typename io_t, bool VEC, bool STORE_HS, bool CHAINED = false>
+// shared memory of sweep_smem_bytes(warps, CB), zero-initialised by the caller.  With STORE_HS every
+// fresh state block is also written to a.hs and d_C is accumulated (backward's recompute sweep).
+// CB = cells per step: each warp advances CB columns of its row between two block barriers (the
+// skew between neighbouring rows is CB columns), which amortises the per-step bookkeeping and lets
+// the exponentials of one cell overlap the recurrence arithmetic of the other.
+template <typename io_t, bool VEC, bool STORE_HS, bool CHAINED = false, int CB = 1>
 __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff, const float4* params,
                                               float D_own, int img0, int img_stride, int nb, int cpos = 0, int chain_arg = 1) {
     const int chain = CHAINED ? chain_arg : 1;   // compile-time 1 in the batch kernels
+    constexpr int SP = 2 * CB * kSlotF4;         // float4 per hand-off slot (two parities x CB cells)
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
     const int g = blockIdx.y, groups = gridDim.y;
@@ -154,13 +158,14 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
     const int W = a.W, H = a.H, E = a.E, Rb = a.Rb, nbands = a.nbands;
+    const int nch = (W + CB - 1) / CB;           // chunks of CB columns per row
     const int nq_c = chain > 1 ? (nbands - cpos + chain - 1) / chain : nbands;   // bands of an image this CTA owns
-    const int T = nb * nq_c * W;              // cells in this warp's sequence
+    const int T = nb * nq_c * nch;               // chunks in this warp's sequence
     const int steps = T + Rb - 1;
     const int pBT = (int)a.pBT, pBL = (int)a.pBL, pC = (int)a.pC;
     float4* const ring = a.ring + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * W) * kSlotF4 + lane;
-    float4* const my = handoff + r * kSlotPair + lane;   // read slot r at my[par*128 + k*32], write slot r+1
-    char* const stage = reinterpret_cast<char*>(handoff + ((blockDim.x >> 5) + 1) * kSlotPair) + r * 2 * kStageBytes;
+    float4* const my = handoff + r * SP + lane;  // read slot r at my[(par*CB + cc)*128 + k*32], write slot r+1
+    char* const stage = reinterpret_cast<char*>(handoff + ((blockDim.x >> 5) + 1) * SP) + r * 2 * CB * kStageBytes;
     const bool y_lane = (g * kGroup + lane) < E;
     const bool ch_copier = (nq == 0) && (chv > 0);   // lanes that copy per-channel / per-state inputs
     const bool st_copier = (cq == 0) && (nv > 0);
@@ -186,7 +191,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
     st.phs = nullptr;
     st.seen = 0; st.pull = ring; st.pcount = nullptr; st.push = ring; st.ccount = nullptr;
 
-    // ---- issue the loads of the next cell of this warp's sequence into `nxt` -------------------
+    // ---- stage the inputs of the next chunk of this warp's sequence -------------------------------
     auto load_phase = [&](int par) {
         if (st.jl == 0) {   // start of a row
             const int q = cpos + st.ql * chain;
@@ -202,34 +207,43 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                 st.seen = 0;
             }
         }
-        if (chain > 1 && st.pull_l && st.seen <= st.jl)
-            st.seen = wait_columns(st.pcount, st.jl + 1, a.status, lane);
-        if (st.row_l) {
-            char* stg = stage + par * kStageBytes;
-            if (VEC) {
-                lc.issue(smem_u32(stg), lane, st.pixl, E);
-            } else {
-                // ragged shapes: one lane per distinct piece, guarded scalar copies (see LaneCopy)
-                const int e0 = st.pixl * E + ch0;
-                stage4<VEC>(ch_copier, stg + cq * 16, static_cast<const io_t*>(a.x), e0, chv);
-                stage4<VEC>(ch_copier, stg + (8 + cq) * 16, static_cast<const io_t*>(a.dT), e0, chv);
-                stage4<VEC>(ch_copier, stg + (16 + cq) * 16, static_cast<const io_t*>(a.dL), e0, chv);
-                if (STORE_HS) stage4<VEC>(ch_copier, stg + (24 + cq) * 16, static_cast<const io_t*>(a.gy), e0, chv);
-                stage4<VEC>(st_copier, stg + (32 + nq) * 16, static_cast<const io_t*>(a.BT), st.pixl * pBT + n0, nv);
-                stage4<VEC>(st_copier, stg + (36 + nq) * 16, static_cast<const io_t*>(a.BL), st.pixl * pBL + n0, nv);
-                stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), st.pixl * pC + n0, nv);
-            }
-            // the row above lives in the previous band: pull it from the ring into slot 0
-            cp_async16x4_if(st.pull_l, smem_u32(my + par * kSlotF4), st.pull + st.jl * kSlotF4);
-            ++st.pixl;
+        const int col0 = st.jl * CB;
+        if (chain > 1 && st.pull_l) {
+            const int need = min(col0 + CB, W);
+            if (st.seen < need) st.seen = wait_columns(st.pcount, need, a.status, lane);
         }
-        if (++st.jl == W) {
+        if (st.row_l) {
+#pragma unroll
+            for (int cc = 0; cc < CB; ++cc) {
+                const int col = col0 + cc;
+                if (CB == 1 || col < W) {
+                    char* stg = stage + (par * CB + cc) * kStageBytes;
+                    if (VEC) {
+                        lc.issue(smem_u32(stg), lane, st.pixl, E);
+                    } else {
+                        // ragged shapes: one lane per distinct piece, guarded scalar copies (see LaneCopy)
+                        const int e0 = st.pixl * E + ch0;
+                        stage4<VEC>(ch_copier, stg + cq * 16, static_cast<const io_t*>(a.x), e0, chv);
+                        stage4<VEC>(ch_copier, stg + (8 + cq) * 16, static_cast<const io_t*>(a.dT), e0, chv);
+                        stage4<VEC>(ch_copier, stg + (16 + cq) * 16, static_cast<const io_t*>(a.dL), e0, chv);
+                        if (STORE_HS) stage4<VEC>(ch_copier, stg + (24 + cq) * 16, static_cast<const io_t*>(a.gy), e0, chv);
+                        stage4<VEC>(st_copier, stg + (32 + nq) * 16, static_cast<const io_t*>(a.BT), st.pixl * pBT + n0, nv);
+                        stage4<VEC>(st_copier, stg + (36 + nq) * 16, static_cast<const io_t*>(a.BL), st.pixl * pBL + n0, nv);
+                        stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), st.pixl * pC + n0, nv);
+                    }
+                    // the row above lives in the previous band: pull it from the ring into slot 0
+                    cp_async16x4_if(st.pull_l, smem_u32(my + (par * CB + cc) * kSlotF4), st.pull + col * kSlotF4);
+                    ++st.pixl;
+                }
+            }
+        }
+        if (++st.jl == nch) {
             st.jl = 0;
             if (++st.ql == nq_c) { st.ql = 0; ++st.bil; }
         }
     };
 
-    // ---- arithmetic of the current cell from `cur`; reads hand-off parity par^1, writes par ----
+    // ---- arithmetic of the current chunk; reads hand-off parity par^1, writes par -------------------
     auto compute_phase = [&](int par) {
         if (st.jc == 0) {
             const int q = cpos + st.qc * chain;
@@ -247,120 +261,127 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
             if (STORE_HS) st.phs = a.hs + (((size_t)b * groups + g) * H * W + (size_t)i * W) * HsBlock<io_t>::f4 + lane;
         }
         if (st.row_c) {
-            const bool first = (st.jc == 0);
-            const float wT = st.row0_c ? 0.f : (first ? 1.f : 0.5f);
-            const float wL = first ? (st.row0_c ? 1.f : 0.f) : (st.row0_c ? 1.f : 0.5f);
-            const float offT = st.row0_c ? ninf : (first ? 0.f : -1.f);
-            const float offL = first ? ninf : (st.row0_c ? 0.f : -1.f);
+            const int col0 = st.jc * CB;
+#pragma unroll
+            for (int cc = 0; cc < CB; ++cc) {
+                const int col = col0 + cc;
+                if (CB == 1 || col < W) {
+                    const bool first = (col == 0);
+                    const float wT = st.row0_c ? 0.f : (first ? 1.f : 0.5f);
+                    const float wL = first ? (st.row0_c ? 1.f : 0.f) : (st.row0_c ? 1.f : 0.5f);
+                    const float offT = st.row0_c ? ninf : (first ? 0.f : -1.f);
+                    const float offL = first ? ninf : (st.row0_c ? 0.f : -1.f);
 
-            float4 top[4];
+                    float4 top[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) top[k] = my[(par ^ 1) * kSlotF4 + k * 32];
-            CellIn cur;   // staged during the previous step
-            {
-                const char* stg = stage + (par ^ 1) * kStageBytes;
-                cur.x = unstage4<io_t>(stg + cq * 16);
-                cur.dT = unstage4<io_t>(stg + (8 + cq) * 16);
-                cur.dL = unstage4<io_t>(stg + (16 + cq) * 16);
-                if (STORE_HS) cur.gy = unstage4<io_t>(stg + (24 + cq) * 16);
-                else cur.gy = make_float4(0.f, 0.f, 0.f, 0.f);
-                cur.bT = unstage4<io_t>(stg + (32 + nq) * 16);
-                cur.bL = unstage4<io_t>(stg + (36 + nq) * 16);
-                cur.c = unstage4<io_t>(stg + (40 + nq) * 16);
-            }
+                    for (int k = 0; k < 4; ++k) top[k] = my[((par ^ 1) * CB + cc) * kSlotF4 + k * 32];
+                    CellIn cur;   // staged during the previous step
+                    {
+                        const char* stg = stage + ((par ^ 1) * CB + cc) * kStageBytes;
+                        cur.x = unstage4<io_t>(stg + cq * 16);
+                        cur.dT = unstage4<io_t>(stg + (8 + cq) * 16);
+                        cur.dL = unstage4<io_t>(stg + (16 + cq) * 16);
+                        if (STORE_HS) cur.gy = unstage4<io_t>(stg + (24 + cq) * 16);
+                        else cur.gy = make_float4(0.f, 0.f, 0.f, 0.f);
+                        cur.bT = unstage4<io_t>(stg + (32 + nq) * 16);
+                        cur.bL = unstage4<io_t>(stg + (36 + nq) * 16);
+                        cur.c = unstage4<io_t>(stg + (40 + nq) * 16);
+                    }
 
-            const float xs[4] = {cur.x.x, cur.x.y, cur.x.z, cur.x.w};
-            const float dTs[4] = {cur.dT.x, cur.dT.y, cur.dT.z, cur.dT.w};
-            const float dLs[4] = {cur.dL.x, cur.dL.y, cur.dL.z, cur.dL.w};
-            const float bTs[4] = {cur.bT.x, cur.bT.y, cur.bT.z, cur.bT.w};
-            const float bLs[4] = {cur.bL.x, cur.bL.y, cur.bL.z, cur.bL.w};
-            const float cs[4] = {cur.c.x, cur.c.y, cur.c.z, cur.c.w};
-            const float gys[4] = {cur.gy.x, cur.gy.y, cur.gy.z, cur.gy.w};
-            float yacc[4];
-            float dC[4] = {0.f, 0.f, 0.f, 0.f};   // recompute sweep only: sum over this thread's channels of gy*h
+                    const float xs[4] = {cur.x.x, cur.x.y, cur.x.z, cur.x.w};
+                    const float dTs[4] = {cur.dT.x, cur.dT.y, cur.dT.z, cur.dT.w};
+                    const float dLs[4] = {cur.dL.x, cur.dL.y, cur.dL.z, cur.dL.w};
+                    const float bTs[4] = {cur.bT.x, cur.bT.y, cur.bT.z, cur.bT.w};
+                    const float bLs[4] = {cur.bL.x, cur.bL.y, cur.bL.z, cur.bL.w};
+                    const float cs[4] = {cur.c.x, cur.c.y, cur.c.z, cur.c.w};
+                    const float gys[4] = {cur.gy.x, cur.gy.y, cur.gy.z, cur.gy.w};
+                    float yacc[4];
+                    float dC[4] = {0.f, 0.f, 0.f, 0.f};   // recompute sweep only: sum over this thread's channels of gy*h
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float tp[4] = {top[c].x, top[c].y, top[c].z, top[c].w};
-                const float4 pT4 = params[c * 32 + lane], pL4 = params[128 + c * 32 + lane];
-                const float aT2c[4] = {pT4.x, pT4.y, pT4.z, pT4.w}, aL2c[4] = {pL4.x, pL4.y, pL4.z, pL4.w};
-                const float dtx = wT * dTs[c] * xs[c];
-                const float dlx = wL * dLs[c] * xs[c];
-                // packed fp32x2 arithmetic (two states per instruction) everywhere except the exponentials
-                float2 acc2 = make_float2(0.f, 0.f);
+                    for (int c = 0; c < 4; ++c) {
+                        const float tp[4] = {top[c].x, top[c].y, top[c].z, top[c].w};
+                        const float4 pT4 = params[c * 32 + lane], pL4 = params[128 + c * 32 + lane];
+                        const float aT2c[4] = {pT4.x, pT4.y, pT4.z, pT4.w}, aL2c[4] = {pL4.x, pL4.y, pL4.z, pL4.w};
+                        const float dtx = wT * dTs[c] * xs[c];
+                        const float dlx = wL * dLs[c] * xs[c];
+                        // packed fp32x2 arithmetic (two states per instruction) everywhere except the exponentials
+                        float2 acc2 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int n = 0; n < 4; n += 2) {
-                    const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), make_float2(aT2c[n], aT2c[n + 1]), make_float2(offT, offT));
-                    const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), make_float2(aL2c[n], aL2c[n + 1]), make_float2(offL, offL));
-                    const float2 gT = make_float2(ex2(argT.x), ex2(argT.y));
-                    const float2 gL = make_float2(ex2(argL.x), ex2(argL.y));
-                    const float2 u = __ffma2_rn(make_float2(dlx, dlx), make_float2(bLs[n], bLs[n + 1]),
-                                                __fmul2_rn(make_float2(dtx, dtx), make_float2(bTs[n], bTs[n + 1])));
-                    const float2 hn = __ffma2_rn(gL, make_float2(h[c][n], h[c][n + 1]),
-                                                 __ffma2_rn(gT, make_float2(tp[n], tp[n + 1]), u));
-                    h[c][n] = hn.x;
-                    h[c][n + 1] = hn.y;
-                    acc2 = __ffma2_rn(hn, make_float2(cs[n], cs[n + 1]), acc2);
+                        for (int n = 0; n < 4; n += 2) {
+                            const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), make_float2(aT2c[n], aT2c[n + 1]), make_float2(offT, offT));
+                            const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), make_float2(aL2c[n], aL2c[n + 1]), make_float2(offL, offL));
+                            const float2 gT = make_float2(ex2(argT.x), ex2(argT.y));
+                            const float2 gL = make_float2(ex2(argL.x), ex2(argL.y));
+                            const float2 u = __ffma2_rn(make_float2(dlx, dlx), make_float2(bLs[n], bLs[n + 1]),
+                                                        __fmul2_rn(make_float2(dtx, dtx), make_float2(bTs[n], bTs[n + 1])));
+                            const float2 hn = __ffma2_rn(gL, make_float2(h[c][n], h[c][n + 1]),
+                                                         __ffma2_rn(gT, make_float2(tp[n], tp[n + 1]), u));
+                            h[c][n] = hn.x;
+                            h[c][n + 1] = hn.y;
+                            acc2 = __ffma2_rn(hn, make_float2(cs[n], cs[n + 1]), acc2);
+                            if (STORE_HS) {
+                                const float2 d2 = __ffma2_rn(make_float2(gys[c], gys[c]), hn, make_float2(dC[n], dC[n + 1]));
+                                dC[n] = d2.x;
+                                dC[n + 1] = d2.y;
+                            }
+                        }
+                        yacc[c] = acc2.x + acc2.y;
+                    }
+
+                    // hand the fresh state to the row below (slot r+1), to the next band, and to the record
+                    {
+                        const float4 h0 = make_float4(h[0][0], h[0][1], h[0][2], h[0][3]), h1 = make_float4(h[1][0], h[1][1], h[1][2], h[1][3]);
+                        const float4 h2 = make_float4(h[2][0], h[2][1], h[2][2], h[2][3]), h3 = make_float4(h[3][0], h[3][1], h[3][2], h[3][3]);
+                        float4* dst = my + SP + (par * CB + cc) * kSlotF4;
+                        dst[0] = h0; dst[32] = h1; dst[64] = h2; dst[96] = h3;
+                        stcg4_if(st.push_c, st.push + col * kSlotF4, h0, h1, h2, h3);
+                        if (STORE_HS) {
+                            if (sizeof(io_t) == 2) {
+                                // bf16 I/O: the record holds bf16 states (the gradients that use it are bf16 anyway)
+                                __stcg(st.phs, make_float4(__uint_as_float(pack_bf16x2(h0.x, h0.y)), __uint_as_float(pack_bf16x2(h0.z, h0.w)),
+                                                           __uint_as_float(pack_bf16x2(h1.x, h1.y)), __uint_as_float(pack_bf16x2(h1.z, h1.w))));
+                                __stcg(st.phs + 32, make_float4(__uint_as_float(pack_bf16x2(h2.x, h2.y)), __uint_as_float(pack_bf16x2(h2.z, h2.w)),
+                                                                __uint_as_float(pack_bf16x2(h3.x, h3.y)), __uint_as_float(pack_bf16x2(h3.z, h3.w))));
+                            } else {
+                                stcg4_if(true, st.phs, h0, h1, h2, h3);
+                            }
+                        }
+                    }
+
                     if (STORE_HS) {
-                        const float2 d2 = __ffma2_rn(make_float2(gys[c], gys[c]), hn, make_float2(dC[n], dC[n + 1]));
-                        dC[n] = d2.x;
-                        dC[n + 1] = d2.y;
-                    }
-                }
-                yacc[c] = acc2.x + acc2.y;
-            }
-
-            // hand the fresh state to the row below (slot r+1), to the next band, and to the record
-            {
-                const float4 h0 = make_float4(h[0][0], h[0][1], h[0][2], h[0][3]), h1 = make_float4(h[1][0], h[1][1], h[1][2], h[1][3]);
-                const float4 h2 = make_float4(h[2][0], h[2][1], h[2][2], h[2][3]), h3 = make_float4(h[3][0], h[3][1], h[3][2], h[3][3]);
-                float4* dst = my + kSlotPair + par * kSlotF4;
-                dst[0] = h0; dst[32] = h1; dst[64] = h2; dst[96] = h3;
-                stcg4_if(st.push_c, st.push + st.jc * kSlotF4, h0, h1, h2, h3);
-                if (chain > 1 && st.push_c) {
-                    // publish the column: data first, then the counter
-                    __threadfence();
-                    __syncwarp();
-                    if (lane == 0) *reinterpret_cast<volatile int*>(st.ccount) = st.jc + 1;
-                }
-                if (STORE_HS) {
-                    if (sizeof(io_t) == 2) {
-                        // bf16 I/O: the record holds bf16 states (the gradients that use it are bf16 anyway)
-                        __stcg(st.phs, make_float4(__uint_as_float(pack_bf16x2(h0.x, h0.y)), __uint_as_float(pack_bf16x2(h0.z, h0.w)),
-                                                   __uint_as_float(pack_bf16x2(h1.x, h1.y)), __uint_as_float(pack_bf16x2(h1.z, h1.w))));
-                        __stcg(st.phs + 32, make_float4(__uint_as_float(pack_bf16x2(h2.x, h2.y)), __uint_as_float(pack_bf16x2(h2.z, h2.w)),
-                                                        __uint_as_float(pack_bf16x2(h3.x, h3.y)), __uint_as_float(pack_bf16x2(h3.z, h3.w))));
+                        // d_C[pixel][n] = sum over channels of gy*h: finish over the 8 cq lanes, then one
+                        // atomic per state from the even-cq lane of each pair
+                        float k0 = hi16 ? dC[2] : dC[0], k1 = hi16 ? dC[3] : dC[1];
+                        k0 += __shfl_xor_sync(0xffffffffu, hi16 ? dC[0] : dC[2], 16);
+                        k1 += __shfl_xor_sync(0xffffffffu, hi16 ? dC[1] : dC[3], 16);
+                        float k = hi8 ? k1 : k0;
+                        k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
+                        k += __shfl_xor_sync(0xffffffffu, k, 4);
+                        if (dc_lane) atomicAdd(a.accC + ((long long)st.pixc * a.N + dc_n), k);
+                        st.phs += HsBlock<io_t>::f4;
                     } else {
-                        stcg4_if(true, st.phs, h0, h1, h2, h3);
+                        const float ysum = reduce_states(yacc[0], yacc[1], yacc[2], yacc[3], nq);
+                        if (y_lane) store1(static_cast<io_t*>(a.y), st.pixc * E + g * kGroup + lane, fmaf(sel4(cur.x, nq), D_own, ysum));
                     }
+                    ++st.pixc;
                 }
             }
-
-            if (STORE_HS) {
-                // d_C[pixel][n] = sum over channels of gy*h: finish over the 8 cq lanes, then one
-                // atomic per state from the even-cq lane of each pair
-                float k0 = hi16 ? dC[2] : dC[0], k1 = hi16 ? dC[3] : dC[1];
-                k0 += __shfl_xor_sync(0xffffffffu, hi16 ? dC[0] : dC[2], 16);
-                k1 += __shfl_xor_sync(0xffffffffu, hi16 ? dC[1] : dC[3], 16);
-                float k = hi8 ? k1 : k0;
-                k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
-                k += __shfl_xor_sync(0xffffffffu, k, 4);
-                if (dc_lane) atomicAdd(a.accC + ((long long)st.pixc * a.N + dc_n), k);
-                st.phs += HsBlock<io_t>::f4;
-            } else {
-                const float ysum = reduce_states(yacc[0], yacc[1], yacc[2], yacc[3], nq);
-                if (y_lane) store1(static_cast<io_t*>(a.y), st.pixc * E + g * kGroup + lane, fmaf(sel4(cur.x, nq), D_own, ysum));
+            if (chain > 1 && st.push_c) {
+                // publish the chunk's columns: data first, then the counter
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) *reinterpret_cast<volatile int*>(st.ccount) = min(col0 + CB, W);
             }
-            ++st.pixc;
         }
-        if (++st.jc == W) {
+        if (++st.jc == nch) {
             st.jc = 0;
             if (++st.qc == nq_c) { st.qc = 0; ++st.bic; }
         }
     };
 
-    // Step s: stage the inputs of cell (s + 1 - r), compute cell (s - r).  s runs from -1 so that the
+    // Step s: stage the inputs of chunk (s + 1 - r), compute chunk (s - r).  s runs from -1 so that the
     // first copy has a step of its own.  Two steps per iteration keep the parity a constant.
-    int cl = -r;     // index of the cell staged in the current step
+    int cl = -r;     // index of the chunk staged in the current step
     for (int s = -1; s < steps; s += 2) {
         if ((unsigned)cl < (unsigned)T) load_phase(1);
         if ((unsigned)(cl - 1) < (unsigned)T) compute_phase(1);

@@ -58,6 +58,7 @@ FWD_SHAPES = [
     (1, 64, 64, 32, 16),
     (1, 200, 136, 64, 16),  # large map, one image: many CTAs chained along the bands of the image
     (2, 96, 40, 32, 16),
+    (1, 2400, 24, 32, 16),  # more bands than resident CTAs: the chain closes into a ring
 ]
 
 
