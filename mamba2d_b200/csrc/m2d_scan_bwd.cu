@@ -1,5 +1,7 @@
 // Backward entry point of the wavefront scan: recompute sweep + adjoint sweep in one kernel,
 // followed by a small kernel that casts the fp32 accumulators of the reduced gradients.
+#include <cstdlib>
+
 #include "plan.cuh"
 #include "sweep_bwd.cuh"
 
@@ -34,7 +36,10 @@ inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
 }
 
 inline Plan plan_bwd(const m2d_scan_desc* d) {
-    Plan p = plan_common(d, 6, 12);
+    // tuning knob: M2D_BWD_WARPS=<1..6> overrides the row-warps per CTA of the backward kernel
+    int maxw = 6;
+    if (const char* e = getenv("M2D_BWD_WARPS")) { const int v = atoi(e); if (v >= 1 && v <= 6) maxw = v; }
+    Plan p = plan_best(d, maxw, 12);
     p.smem = bwd_smem_bytes(p.warps) + kParamF4 * sizeof(float4);
     p.scratch = bwd_layout(d, p).total;
     return p;

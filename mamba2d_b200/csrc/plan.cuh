@@ -93,10 +93,27 @@ inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int warps_per_sm,
     return p;
 }
 
+// Try every cap on the row-warps per CTA and keep the plan that keeps the most warps resident,
+// discounted by the rows lost to padding; ties go to the larger CTA.
+inline Plan plan_best(const m2d_scan_desc* d, int max_warps, int warps_per_sm, int cb = 1) {
+    Plan best = plan_common(d, max_warps, warps_per_sm, cb);
+    double best_score = -1.0;
+    const double cap = (double)warps_per_sm * sm_count();
+    for (int w = max_warps; w >= 2; --w) {
+        const Plan p = plan_common(d, w, warps_per_sm, cb);
+        double resident = (double)p.grid_x * p.groups * p.warps;
+        if (resident > cap) resident = cap;
+        const double eff = (double)d->H / ((double)p.nbands * p.Rb);
+        const double score = resident * eff;
+        if (score > best_score * 1.02) { best_score = score; best = p; }
+    }
+    return best;
+}
+
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 inline Plan plan_fwd(const m2d_scan_desc* d, bool allow_chain = true, bool allow_cb = true) {
-    Plan p = plan_common(d, 8, 16, 1);
+    Plan p = plan_best(d, 8, 16, 1);
     // Few images on a large map: give every image a chain of CTAs, each owning every chain-th band,
     // so that the bands of one image run as a pipeline across SMs.  All CTAs must be resident.
     const long long slots = (long long)(16 / p.warps > 0 ? 16 / p.warps : 1) * sm_count();
@@ -118,7 +135,7 @@ inline Plan plan_fwd(const m2d_scan_desc* d, bool allow_chain = true, bool allow
     if (p.chain == 1 && allow_cb && d->W >= 24) {
         // batch mode: two cells per step where rows are long enough for the band hand-off to stay
         // a step ahead (measured 7 % faster at 56x56 and 28x28; chained launches prefer finer steps)
-        p = plan_common(d, 8, 16, 2);
+        p = plan_best(d, 8, 16, 2);
     }
     if (p.chain > 1) {
         const size_t nband = (size_t)d->B * p.groups * p.nbands;
