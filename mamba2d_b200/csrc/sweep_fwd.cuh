@@ -183,6 +183,15 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
     LaneCopy<io_t> lc;
     lc.init(a.x, a.dT, a.dL, a.gy, a.BT, a.BL, a.C, pBT, pBL, pC, E, a.N, g, lane, STORE_HS);
 
+    // the forward sweep can afford to hold its 32 parameters in registers (the adjoint sweep cannot)
+    float aT2r[4][4], aL2r[4][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const float4 pT4 = params[c * 32 + lane], pL4 = params[128 + c * 32 + lane];
+        aT2r[c][0] = pT4.x; aT2r[c][1] = pT4.y; aT2r[c][2] = pT4.z; aT2r[c][3] = pT4.w;
+        aL2r[c][0] = pL4.x; aL2r[c][1] = pL4.y; aL2r[c][2] = pL4.z; aL2r[c][3] = pL4.w;
+    }
+
     FwdRun st;
     st.jl = st.ql = st.bil = 0;
     st.jc = st.qc = st.bic = 0;
@@ -300,16 +309,14 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const float tp[4] = {top[c].x, top[c].y, top[c].z, top[c].w};
-                        const float4 pT4 = params[c * 32 + lane], pL4 = params[128 + c * 32 + lane];
-                        const float aT2c[4] = {pT4.x, pT4.y, pT4.z, pT4.w}, aL2c[4] = {pL4.x, pL4.y, pL4.z, pL4.w};
                         const float dtx = wT * dTs[c] * xs[c];
                         const float dlx = wL * dLs[c] * xs[c];
                         // packed fp32x2 arithmetic (two states per instruction) everywhere except the exponentials
                         float2 acc2 = make_float2(0.f, 0.f);
 #pragma unroll
                         for (int n = 0; n < 4; n += 2) {
-                            const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), make_float2(aT2c[n], aT2c[n + 1]), make_float2(offT, offT));
-                            const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), make_float2(aL2c[n], aL2c[n + 1]), make_float2(offL, offL));
+                            const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), make_float2(aT2r[c][n], aT2r[c][n + 1]), make_float2(offT, offT));
+                            const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), make_float2(aL2r[c][n], aL2r[c][n + 1]), make_float2(offL, offL));
                             const float2 gT = make_float2(ex2(argT.x), ex2(argT.y));
                             const float2 gL = make_float2(ex2(argL.x), ex2(argL.y));
                             const float2 u = __ffma2_rn(make_float2(dlx, dlx), make_float2(bLs[n], bLs[n + 1]),
