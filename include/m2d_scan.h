@@ -113,6 +113,7 @@ int m2d_scan_fwd(const m2d_scan_desc *desc, void *stream);
  * reference (its launches are serialised by the host).
  */
 int64_t m2d_scan_fwd_status_offset(const m2d_scan_desc *desc);
+int64_t m2d_scan_bwd_status_offset(const m2d_scan_desc *desc);   /* same, for m2d_scan_bwd's workspace */
 
 /*
  * Backward with recomputation of the hidden state: all nine gradients of the forward.

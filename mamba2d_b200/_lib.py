@@ -14,7 +14,7 @@ ABI_VERSION = 1
 NOALLOC_SCRATCH_BYTES = 32 << 20     # M2D_NOALLOC_SCRATCH_BYTES in include/m2d_scan.h
 
 EXPORTS = ("m2d_abi_version", "m2d_strerror", "m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace",
-           "m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc", "m2d_scan_fwd_status_offset")
+           "m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc", "m2d_scan_fwd_status_offset", "m2d_scan_bwd_status_offset")
 
 
 class ScanDesc(ctypes.Structure):
@@ -53,8 +53,9 @@ def lib():
         for name in ("m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace"):
             getattr(L, name).restype = ctypes.c_uint64
             getattr(L, name).argtypes = [ctypes.POINTER(ScanDesc)]
-        L.m2d_scan_fwd_status_offset.restype = ctypes.c_int64
-        L.m2d_scan_fwd_status_offset.argtypes = [ctypes.POINTER(ScanDesc)]
+        for name in ("m2d_scan_fwd_status_offset", "m2d_scan_bwd_status_offset"):
+            getattr(L, name).restype = ctypes.c_int64
+            getattr(L, name).argtypes = [ctypes.POINTER(ScanDesc)]
         for name in ("m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc"):
             getattr(L, name).restype = ctypes.c_int
             getattr(L, name).argtypes = [ctypes.POINTER(ScanDesc), ctypes.c_void_p]

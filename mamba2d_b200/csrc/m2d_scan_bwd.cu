@@ -14,7 +14,7 @@ namespace m2d {
 //          main kernel and cast by a second kernel.  With fp32 I/O the kernel accumulates straight
 //          into the caller's (zeroed) gradient tensors and this region is empty.
 struct BwdLayout {
-    size_t hs, ring, acc, acc_bytes, total;
+    size_t hs, ring, counters, counter_bytes, acc, acc_bytes, total;
 };
 
 inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
@@ -23,7 +23,19 @@ inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
     L.hs = off;
     off += align256((size_t)d->B * p.groups * d->H * d->W * (d->dtype == M2D_F32 ? 128 : 64) * sizeof(float4));
     L.ring = off;
-    if (p.nbands > 1) off += align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
+    L.counters = 0;
+    L.counter_bytes = 0;
+    if (p.chain > 1) {
+        // chained CTAs: one boundary row per band (h downwards in the recompute sweep, pT upwards in the
+        // adjoint sweep), two column counters per band and a status word
+        const size_t nband = (size_t)d->B * p.groups * p.nbands;
+        off += align256(nband * d->W * kSlotF4 * sizeof(float4));
+        L.counters = off;
+        L.counter_bytes = align256((2 * nband + 1) * sizeof(int));
+        off += L.counter_bytes;
+    } else if (p.nbands > 1) {
+        off += align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
+    }
     L.acc = off;
     L.acc_bytes = 0;
     if (d->dtype != M2D_F32) {
@@ -41,11 +53,25 @@ inline Plan plan_bwd(const m2d_scan_desc* d) {
     if (const char* e = getenv("M2D_BWD_WARPS")) { const int v = atoi(e); if (v >= 1 && v <= 6) maxw = v; }
     Plan p = plan_best(d, maxw, 12);
     p.smem = bwd_smem_bytes(p.warps) + kParamF4 * sizeof(float4);
+    // few images on a large map: chain CTAs along the bands of an image, as the forward does
+    {
+        const long long slots = (long long)(12 / p.warps > 0 ? 12 / p.warps : 1) * sm_count();
+        const long long ctas = (long long)p.grid_x * p.groups;
+        if (p.nbands > 1 && ctas * 2 <= slots) {
+            long long c = slots / ctas;
+            if (c > p.nbands) c = p.nbands;
+            if (c < p.nbands) {
+                const long long lim = d->W / p.Rb - 1;   // ring bound, see plan_fwd
+                if (c > lim) c = lim;
+            }
+            p.chain = c < 1 ? 1 : (int)c;
+        }
+    }
     p.scratch = bwd_layout(d, p).total;
     return p;
 }
 
-template <typename io_t, bool VEC>
+template <typename io_t, bool VEC, bool CHAINED>
 __global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
     extern __shared__ float4 handoff[];
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
@@ -73,9 +99,12 @@ __global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
     if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane);
     __syncthreads();
 
-    for (int b = blockIdx.x; b < a.B; b += gridDim.x) {
-        forward_sweep<io_t, VEC, true>(a, handoff, params, D_own, b, 0, 1);
-        reverse_sweep<io_t, VEC>(a, handoff, params, D_own, dAT, dAL, dD, b);
+    // gridDim.x = chains x a.chain: CTA (chain_id, cpos) walks images chain_id, chain_id + chains, ...
+    const int chains = (int)gridDim.x / a.chain;
+    const int chain_id = (int)blockIdx.x / a.chain, cpos = (int)blockIdx.x % a.chain;
+    for (int b = chain_id; b < a.B; b += chains) {
+        forward_sweep<io_t, VEC, true, CHAINED, 1>(a, handoff, params, D_own, b, 0, 1, cpos, a.chain);
+        reverse_sweep<io_t, VEC, CHAINED>(a, handoff, params, D_own, dAT, dAL, dD, b, cpos, a.chain);
     }
 
     // ---- per-(channel,state) sums: fold the CTA's row-warps through shared memory, then one
@@ -152,7 +181,14 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     a.y = nullptr;
     a.ring = reinterpret_cast<float4*>(ws + L.ring);
     a.Rb = pl.Rb; a.nbands = pl.nbands;
-    a.chain = 1; a.bnd = nullptr; a.progress = nullptr; a.status = nullptr;
+    a.chain = pl.chain; a.bnd = nullptr; a.progress = nullptr; a.status = nullptr;
+    if (pl.chain > 1) {
+        const size_t nband = (size_t)d->B * pl.groups * pl.nbands;
+        a.bnd = reinterpret_cast<float4*>(ws + L.ring);
+        a.progress = reinterpret_cast<int*>(ws + L.counters);
+        a.status = a.progress + 2 * nband;
+        if (cudaMemsetAsync(a.progress, 0, (2 * nband + 1) * sizeof(int), st) != cudaSuccess) return M2D_ERR_LAUNCH;
+    }
     a.gy = d->gy;
     a.hs = reinterpret_cast<float4*>(ws + L.hs);
     a.d_x = d->d_x; a.d_dT = d->d_dT; a.d_dL = d->d_dL;
@@ -170,13 +206,34 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
         a.accAT = acc + 3 * npn; a.accAL = a.accAT + en; a.accD = a.accAL + en;
         if (cudaMemsetAsync(acc, 0, L.acc_bytes, st) != cudaSuccess) return M2D_ERR_LAUNCH;
     }
-    dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
-    auto kern = vec ? m2d_bwd_kernel<io_t, true> : m2d_bwd_kernel<io_t, false>;
+    dim3 block(pl.warps * 32);
+    void (*kern)(const ScanArgs) = pl.chain > 1 ? (vec ? m2d_bwd_kernel<io_t, true, true> : m2d_bwd_kernel<io_t, false, true>)
+                                                : (vec ? m2d_bwd_kernel<io_t, true, false> : m2d_bwd_kernel<io_t, false, false>);
     if (pl.smem > 48 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
         return M2D_ERR_LAUNCH;
-    kern<<<grid, block, pl.smem, st>>>(a);
-    if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
+    if (a.chain > 1) {
+        // cooperative launch: every CTA of a chain must be resident (see the forward launch)
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)block.x, pl.smem) != cudaSuccess || per_sm < 1)
+            return M2D_ERR_LAUNCH;
+        const long long fit = (long long)per_sm * sm_count() / ((long long)pl.grid_x * pl.groups);
+        if (fit < a.chain) a.chain = fit < 1 ? 1 : (int)fit;
+        for (;;) {
+            dim3 grid(pl.grid_x * a.chain, pl.groups);
+            void* args[] = {&a};
+            const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), grid, block, args, pl.smem, st);
+            if (e == cudaSuccess) break;
+            cudaGetLastError();
+            if (e != cudaErrorCooperativeLaunchTooLarge || a.chain == 1) return M2D_ERR_LAUNCH;
+            a.chain = a.chain > 2 ? a.chain - a.chain / 4 - 1 : 1;
+        }
+    } else {
+        dim3 grid(pl.grid_x, pl.groups);
+        kern<<<grid, block, pl.smem, st>>>(a);
+        if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
+    }
     if (d->dtype != M2D_F32) {
         const int fin_blocks = (int)((npn + 255) / 256 < 148 * 8 ? (npn + 255) / 256 : 148 * 8);
         m2d_bwd_finalize<io_t><<<fin_blocks, 256, 0, st>>>(a.accBT, static_cast<io_t*>(d->d_BT), static_cast<io_t*>(d->d_BL),
@@ -193,6 +250,14 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
 extern "C" uint64_t m2d_scan_bwd_workspace(const m2d_scan_desc* d) {
     if (m2d::check_desc(d, true, false) != M2D_OK) return 0;
     return m2d::plan_bwd(d).scratch;
+}
+
+extern "C" int64_t m2d_scan_bwd_status_offset(const m2d_scan_desc* d) {
+    if (m2d::check_desc(d, true, false) != M2D_OK) return -1;
+    const m2d::Plan pl = m2d::plan_bwd(d);
+    if (pl.chain <= 1) return -1;
+    const m2d::BwdLayout L = m2d::bwd_layout(d, pl);
+    return (int64_t)(L.counters + 2 * (size_t)d->B * pl.groups * pl.nbands * sizeof(int));
 }
 
 extern "C" int m2d_scan_bwd(const m2d_scan_desc* d, void* stream) {

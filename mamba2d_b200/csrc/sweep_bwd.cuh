@@ -36,8 +36,13 @@ namespace m2d {
 __host__ __device__ inline size_t bwd_smem_bytes(int warps) { return sweep_smem_bytes(warps) + handoff_bytes(warps); }   // + parameters behind
 
 struct RevRun {
-    int pixl, jl, ql;       // load side (reversed counters: jl = W-1-j, ql = nbands-1-q)
+    int pixl, jl, ql;       // load side (reversed counters: jl = W-1-j, ql counts this CTA's bands from its last)
     bool row_l, pull_l, top_l;
+    int seen;               // columns of the band below known to be published (chained CTAs)
+    const float4* pull;     // pT row of the band below
+    const int* pcount;      // its column counter
+    float4* push;           // where this band's first row puts its pT
+    int* ccount;            // its column counter
     const float4* phl;      // state record of h[i][j-1] for the cell being staged
     int pixc, jc, qc;       // compute side
     bool row_c, push_c, bottom_c, row0_c;
@@ -45,10 +50,11 @@ struct RevRun {
 };
 
 // One CTA's adjoint sweep over image `b`.  dAT/dAL/dD accumulate across calls.
-template <typename io_t, bool VEC>
+template <typename io_t, bool VEC, bool CHAINED = false>
 __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff, const float4* params,
                                               float D_own, float (&dAT)[4][4],
-                                              float (&dAL)[4][4], float (&dD)[4], int b) {
+                                              float (&dAL)[4][4], float (&dD)[4], int b, int cpos = 0, int chain_arg = 1) {
+    const int chain = CHAINED ? chain_arg : 1;
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
@@ -58,7 +64,8 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
     const int nv = min(4, max(0, a.N - n0));
     const int W = a.W, H = a.H, E = a.E, Rb = a.Rb, nbands = a.nbands;
     const int rr = Rb - 1 - r;                 // rank in the reverse sweep
-    const int T = nbands * W;
+    const int nq_c = chain > 1 ? (nbands - cpos + chain - 1) / chain : nbands;   // bands this CTA owns
+    const int T = nq_c * W;
     const int steps = T + Rb - 1;
     const int pBT = (int)a.pBT, pBL = (int)a.pBL, pC = (int)a.pC;
     float4* const ring = a.ring + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * W) * kSlotF4 + lane;
@@ -94,6 +101,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
     st.pixc = st.jc = st.qc = 0;
     st.row_l = st.pull_l = st.top_l = st.row_c = st.push_c = st.bottom_c = st.row0_c = false;
     st.phl = nullptr;
+    st.seen = 0; st.pull = ring; st.pcount = nullptr; st.push = ring; st.ccount = nullptr;
     st.cfac = st.mT = st.mL = st.offT = st.offL = 0.f;
 
     // One state-record block, global -> shared (2 KiB of fp32 states or 1 KiB of bf16 states).
@@ -123,15 +131,25 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
     // ---- stage the inputs and h[i][j-1] (and h[i-1][j] for the top row of a band) of the next cell
     auto load_phase = [&](int par) {
         if (st.jl == 0) {   // start of a row (its right end)
-            const int q = nbands - 1 - st.ql;
+            const int q = cpos + (nq_c - 1 - st.ql) * chain;
             const int i = q * Rb + r;
             st.row_l = (r < Rb) && (i < H);
             st.pull_l = st.row_l && (rr == 0) && (i + 1 < H);      // pT of the row below comes through the ring
+            if (chain > 1 && q + 1 < nbands) {
+                // the band below belongs to another CTA: its pT row sits in the boundary slot between
+                // band q and band q+1 (the slot the forward sweep used for h in the other direction)
+                const size_t band = ((size_t)b * groups + g) * nbands + q;
+                st.pull = a.bnd + band * W * kSlotF4 + lane;
+                st.pcount = a.progress + (size_t)a.B * groups * nbands + band + 1;
+                st.seen = 0;
+            }
             st.top_l = st.row_l && (r == 0) && (i > 0);            // h of the row above is not in this band
             st.pixl = (b * H + i) * W + (W - 1);
             st.phl = hs_img + ((size_t)i * W + (W - 2)) * HB;
         }
         const int j = W - 1 - st.jl;
+        if (chain > 1 && st.pull_l && st.seen < st.jl + 1)
+            st.seen = wait_columns(st.pcount, st.jl + 1, a.status, lane);
         if (st.row_l) {
             char* stg = stage + par * kStageBytes;
             if (VEC) {
@@ -148,22 +166,27 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
             }
             copy_block(j > 0, smem_u32(h_own + par * kSlotF4), st.phl);
             copy_block(st.top_l, smem_u32(h_up + par * kSlotF4), st.phl + (ptrdiff_t)(1 - W) * HB);
-            cp_async16x4_if(st.pull_l, smem_u32(my + par * kSlotF4), ring + j * kSlotF4);
+            cp_async16x4_if(st.pull_l, smem_u32(my + par * kSlotF4), st.pull + j * kSlotF4);
             --st.pixl;
             st.phl -= HB;
         }
         // last cell of a row: its own h[i][-1] does not exist (that gate is zero), so the slot is
         // free for the right-most block of the row this warp starts next
-        if (j == 0 && st.ql + 1 < nbands) prefetch_row_end(nbands - 2 - st.ql, par);
+        if (j == 0 && st.ql + 1 < nq_c) prefetch_row_end(cpos + (nq_c - 2 - st.ql) * chain, par);
         if (++st.jl == W) { st.jl = 0; ++st.ql; }
     };
 
     // ---- adjoint arithmetic of the current cell ---------------------------------------------------
     auto compute_phase = [&](int par) {
         if (st.jc == 0) {
-            const int q = nbands - 1 - st.qc;
+            const int q = cpos + (nq_c - 1 - st.qc) * chain;
             const int i = q * Rb + r;
             st.row_c = (r < Rb) && (i < H);
+            if (chain > 1 && q > 0) {
+                const size_t band = ((size_t)b * groups + g) * nbands + q;
+                st.push = a.bnd + (band - 1) * W * kSlotF4 + lane;
+                st.ccount = a.progress + (size_t)a.B * groups * nbands + band;
+            }
             st.row0_c = (i == 0);
             st.bottom_c = (i + 1 >= H);
             st.push_c = st.row_c && (r == 0) && (q > 0);
@@ -251,12 +274,19 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 // pT goes to the row above: next rank's slot, and the ring when that row is in another band
                 const float4 pT4 = make_float4(pt[0], pt[1], pt[2], pt[3]);
                 my[kSlotPair + par * kSlotF4 + c * 32] = pT4;
-                stcg_if(st.push_c, ring + j * kSlotF4 + c * 32, pT4);
+                stcg_if(st.push_c, st.push + j * kSlotF4 + c * 32, pT4);
                 const float qT = qT2.x + qT2.y, qL = qL2.x + qL2.y, sT = sT2.x + sT2.y, sL = sL2.x + sL2.y;
                 o_dT[c] = fmaf(qT, kLn2, mT * xs[c] * sT);
                 o_dL[c] = fmaf(qL, kLn2, mL * xs[c] * sL);
                 o_dx[c] = fmaf(mT * dTs[c], sT, mL * dLs[c] * sL);
                 dD[c] = fmaf(gys[c], xs[c], dD[c]);
+            }
+
+            if (chain > 1 && st.push_c) {
+                // publish the column (columns are produced right to left): data first, then the counter
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) *reinterpret_cast<volatile int*>(st.ccount) = st.jc + 1;
             }
 
             // sums over states: 2-step exchange over the nq lanes; lane l ends with channel l of the group
@@ -300,14 +330,14 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
     int cl = -rr;
     for (int s = -1; s < steps; s += 2) {
         if ((unsigned)cl < (unsigned)T) load_phase(1);
-        else if (cl == -1) prefetch_row_end(nbands - 1, 1);
+        else if (cl == -1) prefetch_row_end(cpos + (nq_c - 1) * chain, 1);
         if ((unsigned)(cl - 1) < (unsigned)T) compute_phase(1);
         ++cl;
         cp_async_wait_all();
         __syncthreads();
         if (s + 1 < steps) {
             if ((unsigned)cl < (unsigned)T) load_phase(0);
-            else if (cl == -1) prefetch_row_end(nbands - 1, 0);
+            else if (cl == -1) prefetch_row_end(cpos + (nq_c - 1) * chain, 0);
             if ((unsigned)(cl - 1) < (unsigned)T) compute_phase(0);
             ++cl;
             cp_async_wait_all();

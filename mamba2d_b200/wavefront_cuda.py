@@ -143,6 +143,10 @@ def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output):
         _workspace(d, L.m2d_scan_bwd_workspace(ctypes.byref(d)), dev, keep)
         rc = L.m2d_scan_bwd(ctypes.byref(d), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     _lib.check(rc, "m2d_scan_bwd")
+    if _CHECK_STATUS:
+        off = L.m2d_scan_bwd_status_offset(ctypes.byref(d))
+        if off >= 0 and keep[-1][off:off + 4].view(torch.int32).item() != 0:
+            raise RuntimeError("m2d_scan_bwd: a wait between CTAs of one image timed out; the gradients are invalid")
     return outs
 
 

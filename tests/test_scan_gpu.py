@@ -108,6 +108,9 @@ BWD_SHAPES = [
     (1, 9, 13, 40, 12),
     (1, 13, 3, 32, 16),
     (5, 3, 19, 32, 8),
+    (1, 120, 72, 64, 16),   # large map, one image: chained CTAs in both sweeps of the backward
+    (2, 96, 40, 32, 16),
+    (1, 2000, 20, 32, 16),  # more bands than resident CTAs: the chain closes into a ring
 ]
 
 
