@@ -1,0 +1,114 @@
+"""Run one shape of the scan a few times on the current GPU: the command line used for ncu
+captures and for one-off timings.
+
+    python -m mamba2d_b200.profile_case --shape 128,56,56,64 [--dtype f32|bf16] [--bwd] [--iters 3]
+    python -m mamba2d_b200.profile_case --sweep 64,128,256,512,1024 [--reference]
+    python -m mamba2d_b200.profile_case --shape 2,200,336,64 --bwd --time [--reference]
+
+Inputs are seeded synthetic tensors (N = 16 states, BT/BL/C as strided views of one projection
+buffer).  ``--time`` prints CUDA-event timings; ``--reference`` also times the reference
+project's own CUDA extension when it has been prebuilt (oracle/_ref/), for comparison.
+"""
+import argparse
+import math
+import os
+import sys
+
+import torch
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORDER = ("x", "dT", "dL", "AT", "AL", "BT", "BL", "C", "D")
+
+
+def make_inputs(B, H, W, E, N=16, seed=0, dtype=torch.float32, device="cuda", strided=True):
+    """Same draws, in the same order, as the test-suite generator (x, dT, dL, BT, BL, C, AT, AL, D, gy)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn(B, H, W, E, generator=g)
+    dT = F.softplus(torch.randn(B, H, W, E, generator=g) * 0.5 - 2.0)
+    dL = F.softplus(torch.randn(B, H, W, E, generator=g) * 0.5 - 2.0)
+    std = N ** -0.5
+    BT, BL, C = (torch.randn(B, H, W, N, generator=g) * std for _ in range(3))
+    AT = -torch.exp(torch.rand(E, N, generator=g) * math.log(16.0))
+    AL = -torch.exp(torch.rand(E, N, generator=g) * math.log(16.0))
+    D = torch.randn(E, generator=g)
+    gy = torch.randn(B, H, W, E, generator=g)
+    out = {k: v.to(device, dtype) for k, v in dict(x=x, dT=dT, dL=dL, AT=AT, AL=AL, D=D, gy=gy).items()}
+    if strided:
+        R = math.ceil(E / 16)
+        buf = torch.zeros(B, H, W, 2 * R + 3 * N)
+        buf[..., 2 * R:2 * R + N], buf[..., 2 * R + N:2 * R + 2 * N], buf[..., 2 * R + 2 * N:] = BT, BL, C
+        buf = buf.to(device, dtype)
+        out["BT"], out["BL"], out["C"] = buf[..., 2 * R:2 * R + N], buf[..., 2 * R + N:2 * R + 2 * N], buf[..., 2 * R + 2 * N:]
+    else:
+        out["BT"], out["BL"], out["C"] = (t.to(device, dtype) for t in (BT, BL, C))
+    return out
+
+
+def timeit(fn, iters, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def reference_ext():
+    sys.path.insert(0, ROOT)
+    try:
+        from oracle import ref_gpu          # optional comparison only; never used by the product path
+        return ref_gpu if ref_gpu.available() else None
+    except Exception:
+        return None
+
+
+def run_case(B, H, W, E, dtype, bwd, iters, timed, with_ref):
+    from mamba2d_b200 import scan_bwd, scan_fwd
+    d = make_inputs(B, H, W, E, dtype=dtype)
+    a = [d[k] for k in ORDER]
+    if not timed:
+        for _ in range(iters):
+            scan_fwd(*a)
+            if bwd:
+                scan_bwd(*a, d["gy"])
+        torch.cuda.synchronize()
+        print("ok")
+        return
+    line = f"B={B} {H}x{W} E={E} {str(dtype).split('.')[-1]}: fwd {timeit(lambda: scan_fwd(*a), iters):.3f} ms"
+    if bwd:
+        line += f", bwd {timeit(lambda: scan_bwd(*a, d['gy']), iters):.3f} ms"
+    ref = reference_ext() if with_ref else None
+    if ref is not None:
+        c = [t.contiguous() for t in a]
+        line += f" | reference extension fwd {timeit(lambda: ref.forward(*c), iters):.3f} ms"
+        if bwd:
+            line += f", bwd {timeit(lambda: ref.backward(*c, d['gy']), iters):.3f} ms"
+    print(line, flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", default="128,56,56,64", help="B,H,W,E")
+    ap.add_argument("--sweep", default=None, help="comma-separated H=W values at B=1, E=64 (forward)")
+    ap.add_argument("--dtype", choices=("f32", "bf16"), default="f32")
+    ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--time", action="store_true")
+    ap.add_argument("--reference", action="store_true")
+    args = ap.parse_args()
+    dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
+    if args.sweep:
+        for hw in (int(v) for v in args.sweep.split(",")):
+            run_case(1, hw, hw, 64, dtype, False, args.iters, True, args.reference and hw <= 1024)
+        return
+    B, H, W, E = (int(v) for v in args.shape.split(","))
+    run_case(B, H, W, E, dtype, args.bwd, args.iters, args.time, args.reference)
+
+
+if __name__ == "__main__":
+    main()
