@@ -39,7 +39,7 @@ BYTES = {"f32": 4, "bf16": 2}
 
 # DRAM bytes (read + write) of ONE launch of the dominant kernel, from an ncu capture of this same
 # workload; see profiles/ for the capture summaries.  None = not captured for that dtype.
-NCU_TRAFFIC = {"f32": 6.342e9, "bf16": None}   # profiles/m2d_bwd_kernel_f32_D64_56x56.md
+NCU_TRAFFIC = {"f32": 6.097e9, "bf16": None}   # profiles/m2d_bwd_kernel_f32_D64_56x56.md
 
 
 def fwd_bytes(D, HW, s, B=BATCH, N=NSTATE):
