@@ -297,8 +297,8 @@ def cpu_baseline(dtype, sample_batch=64, repeat=1, threads=None):
     import torch
     from oracle import cpu as ocpu
     from oracle import inputs as oin
-    if threads:
-        ocpu.set_threads(threads)
+    # all host cores this process may use (torchrun presets OMP_NUM_THREADS=1 for its ranks)
+    ocpu.set_threads(threads or len(os.sched_getaffinity(0)))
     cores = ocpu.num_threads()
     el = 0
     t = 0.0
