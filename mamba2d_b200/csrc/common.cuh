@@ -25,14 +25,6 @@ __device__ __forceinline__ float ex2(float v) {
     return r;
 }
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
-    unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(s), "l"(gmem) : "memory");
-}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // Predicated forms (no branch, no reconvergence point): the copy / store happens iff `on`.
@@ -164,33 +156,8 @@ template <> __device__ __forceinline__ float4 unstage4<__nv_bfloat16>(const char
                        __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
 }
 
-// ---- element loads: four consecutive elements as floats, zero beyond `nvalid` ----------------
-template <bool VEC>
-__device__ __forceinline__ float4 load4(const float* __restrict__ p, long long off, int nvalid) {
-    if (VEC) return __ldg(reinterpret_cast<const float4*>(p + off));
-    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (nvalid > 0) r.x = __ldg(p + off);
-    if (nvalid > 1) r.y = __ldg(p + off + 1);
-    if (nvalid > 2) r.z = __ldg(p + off + 2);
-    if (nvalid > 3) r.w = __ldg(p + off + 3);
-    return r;
-}
+// ---- scalar element loads / stores --------------------------------------------------------------
 __device__ __forceinline__ float bf16_bits_to_float(unsigned short b) { return __uint_as_float(static_cast<unsigned>(b) << 16); }
-template <bool VEC>
-__device__ __forceinline__ float4 load4(const __nv_bfloat16* __restrict__ p, long long off, int nvalid) {
-    if (VEC) {
-        const uint2 u = __ldg(reinterpret_cast<const uint2*>(p + off));
-        return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
-                           __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
-    }
-    const unsigned short* q = reinterpret_cast<const unsigned short*>(p) + off;
-    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (nvalid > 0) r.x = bf16_bits_to_float(__ldg(q));
-    if (nvalid > 1) r.y = bf16_bits_to_float(__ldg(q + 1));
-    if (nvalid > 2) r.z = bf16_bits_to_float(__ldg(q + 2));
-    if (nvalid > 3) r.w = bf16_bits_to_float(__ldg(q + 3));
-    return r;
-}
 __device__ __forceinline__ float load1(const float* __restrict__ p, long long off) { return __ldg(p + off); }
 __device__ __forceinline__ float load1(const __nv_bfloat16* __restrict__ p, long long off) {
     return bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(p) + off));
@@ -213,21 +180,6 @@ __device__ __forceinline__ float reduce_states(float v0, float v1, float v2, flo
     const bool hi1 = (nq & 1) != 0;
     const float k = hi1 ? k1 : k0, s = hi1 ? k0 : k1;
     return k + __shfl_xor_sync(0xffffffffu, s, 1);
-}
-
-// Cell position inside a CTA's work list.  A CTA walks `nb` images; each image is cut into
-// `nbands` bands of `Rb` rows; warp r of the CTA owns row q*Rb + r of band q and walks its W
-// columns, one per step, lagging r steps behind warp 0 so that the row above is always one step
-// ahead (the anti-diagonal wavefront).
-struct Pos {
-    int j, q, bi;
-};
-__device__ __forceinline__ Pos advance(Pos a, int W, int nbands) {
-    if (++a.j == W) {
-        a.j = 0;
-        if (++a.q == nbands) { a.q = 0; ++a.bi; }
-    }
-    return a;
 }
 
 // Host-side launch plan shared by the workspace queries and the launches.

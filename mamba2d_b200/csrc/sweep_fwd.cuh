@@ -87,16 +87,6 @@ struct CellIn {
     float4 gy;   // only loaded by the backward sweeps
 };
 
-// Load the thread's 4x4 block of a (E,N) parameter, scaled; zero outside the valid range.
-template <typename io_t>
-__device__ __forceinline__ void load_param_block(float (&dst)[4][4], const void* P, int N, int ch0, int chv, int n0, int nv, float scale) {
-#pragma unroll
-    for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int n = 0; n < 4; ++n)
-            dst[c][n] = (c < chv && n < nv) ? load1(static_cast<const io_t*>(P), (long long)(ch0 + c) * N + n0 + n) * scale : 0.f;
-}
-
 // Bounded wait of a consumer warp on a producer's column counter (another CTA).  Returns the value
 // seen; after kWaitPolls unsuccessful polls it records the failure in *status and gives up, so a
 // kernel can never spin forever.
