@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define M2D_ABI_VERSION 1
+#define M2D_ABI_VERSION 2
 
 typedef enum m2d_dtype {
     M2D_F32 = 0,   /* float in memory, float arithmetic */
@@ -49,9 +49,24 @@ typedef enum m2d_status {
     M2D_ERR_WORKSPACE = -6,     /* workspace missing, too small or not 256-byte aligned */
     M2D_ERR_LAUNCH = -7,        /* the CUDA runtime rejected a launch or a memset */
     M2D_ERR_ABI = -8,           /* descriptor size does not match this library */
-    M2D_ERR_TOO_LARGE = -9      /* B*H*W*max(E, pitch) >= 2^31 (kernels use 31-bit element indices), or
+    M2D_ERR_TOO_LARGE = -9,     /* B*H*W*max(E, pitch) >= 2^31 (kernels use 31-bit element indices), or
                                    scratch beyond the capacity of the no-allocation entry point */
+    M2D_ERR_FLAGS = -10         /* an unknown bit is set in desc->flags */
 } m2d_status;
+
+/*
+ * desc->flags bits.
+ *
+ * M2D_SCAN_REVERSE: scan from the bottom-right corner towards the top-left one.  The result is
+ * what the forward-direction call returns on inputs whose H and W axes are both flipped, flipped
+ * back -- for y and for every gradient -- but no tensor is copied: the kernels walk the same
+ * memory in the opposite order.  The reference gets this direction with torch.flip copies of the
+ * activation around the whole block (scan_start == "BR", models/mamba2d.py:162-175, chosen for odd
+ * blocks by inter_flip, :350) and around the second scan of double_scans (:190-200); everything
+ * between those flips other than the scan acts per pixel, so the flips can be dropped when the
+ * scan itself runs in reverse.
+ */
+#define M2D_SCAN_REVERSE 1u
 
 /*
  * Problem descriptor.  Tensor layouts are the ones the reference op receives:
@@ -70,7 +85,7 @@ typedef struct m2d_scan_desc {
     uint32_t struct_bytes;      /* = sizeof(m2d_scan_desc) */
     int32_t dtype;              /* m2d_dtype */
     int32_t B, H, W, E, N;
-    int32_t reserved0;
+    uint32_t flags;             /* 0 or M2D_SCAN_* bits */
     const void *x, *dT, *dL;
     const void *AT, *AL;
     const void *BT, *BL, *C;

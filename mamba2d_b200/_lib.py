@@ -10,7 +10,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("M2D_SCAN_LIB", os.path.join(HERE, "libm2d_scan.so"))   # override: an alternative build of the same ABI
 
 M2D_F32, M2D_BF16 = 0, 1
-ABI_VERSION = 1
+M2D_SCAN_REVERSE = 1
+ABI_VERSION = 2
 NOALLOC_SCRATCH_BYTES = 32 << 20     # M2D_NOALLOC_SCRATCH_BYTES in include/m2d_scan.h
 
 EXPORTS = ("m2d_abi_version", "m2d_strerror", "m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace",
@@ -22,7 +23,7 @@ class ScanDesc(ctypes.Structure):
     _fields_ = [
         ("struct_bytes", ctypes.c_uint32), ("dtype", ctypes.c_int32),
         ("B", ctypes.c_int32), ("H", ctypes.c_int32), ("W", ctypes.c_int32), ("E", ctypes.c_int32), ("N", ctypes.c_int32),
-        ("reserved0", ctypes.c_int32),
+        ("flags", ctypes.c_uint32),
         ("x", ctypes.c_void_p), ("dT", ctypes.c_void_p), ("dL", ctypes.c_void_p),
         ("AT", ctypes.c_void_p), ("AL", ctypes.c_void_p),
         ("BT", ctypes.c_void_p), ("BL", ctypes.c_void_p), ("C", ctypes.c_void_p),

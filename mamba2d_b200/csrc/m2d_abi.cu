@@ -15,6 +15,7 @@ extern "C" const char* m2d_strerror(int status) {
         case M2D_ERR_LAUNCH: return "CUDA launch failed";
         case M2D_ERR_ABI: return "descriptor size does not match this library";
         case M2D_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of this entry point";
+        case M2D_ERR_FLAGS: return "unknown bit in desc->flags";
         default: return "unknown status";
     }
 }

@@ -35,6 +35,7 @@ template <typename io_t>
 static int launch_fwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStream_t st) {
     FwdArgs a;
     a.B = d->B; a.H = d->H; a.W = d->W; a.E = d->E; a.N = d->N;
+    a.dir = (d->flags & M2D_SCAN_REVERSE) ? -1 : 1;
     a.x = d->x; a.dT = d->dT; a.dL = d->dL; a.AT = d->AT; a.AL = d->AL;
     a.BT = d->BT; a.BL = d->BL; a.C = d->C; a.D = d->D;
     a.pBT = d->BT_pitch; a.pBL = d->BL_pitch; a.pC = d->C_pitch;

@@ -18,6 +18,7 @@ inline int check_desc(const m2d_scan_desc* d, bool bwd, bool need_ptrs) {
     if (!d) return M2D_ERR_NULL;
     if (d->struct_bytes != sizeof(m2d_scan_desc)) return M2D_ERR_ABI;
     if (d->dtype != M2D_F32 && d->dtype != M2D_BF16) return M2D_ERR_DTYPE;
+    if (d->flags & ~M2D_SCAN_REVERSE) return M2D_ERR_FLAGS;
     if (d->B < 1 || d->E < 1 || d->N < 1 || d->H < 2 || d->W < 2) return M2D_ERR_SHAPE;
     if (d->N > kMaxN) return M2D_ERR_UNSUPPORTED_N;
     if (d->BT_pitch < d->N || d->BL_pitch < d->N || d->C_pitch < d->N) return M2D_ERR_PITCH;

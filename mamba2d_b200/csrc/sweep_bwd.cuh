@@ -144,7 +144,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 st.seen = 0;
             }
             st.top_l = st.row_l && (r == 0) && (i > 0);            // h of the row above is not in this band
-            st.pixl = (b * H + i) * W + (W - 1);
+            st.pixl = scan_pixel(a, b, i, W - 1);
             st.phl = hs_img + ((size_t)i * W + (W - 2)) * HB;
         }
         const int j = W - 1 - st.jl;
@@ -167,7 +167,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
             copy_block(j > 0, smem_u32(h_own + par * kSlotF4), st.phl);
             copy_block(st.top_l, smem_u32(h_up + par * kSlotF4), st.phl + (ptrdiff_t)(1 - W) * HB);
             cp_async16x4_if(st.pull_l, smem_u32(my + par * kSlotF4), st.pull + j * kSlotF4);
-            --st.pixl;
+            st.pixl -= a.dir;
             st.phl -= HB;
         }
         // last cell of a row: its own h[i][-1] does not exist (that gate is zero), so the slot is
@@ -190,7 +190,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
             st.row0_c = (i == 0);
             st.bottom_c = (i + 1 >= H);
             st.push_c = st.row_c && (r == 0) && (q > 0);
-            st.pixc = (b * H + i) * W + (W - 1);
+            st.pixc = scan_pixel(a, b, i, W - 1);
             // columns j > 0: interior unless on row 0
             st.cfac = st.row0_c ? 1.f : 0.5f;
             st.mT = st.row0_c ? 0.f : 1.f;
@@ -320,7 +320,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 // this lane now owns array (hi16 ? d_BL : d_BT), state n0 + 2*hi8 + hi4
                 if (db_lane) atomicAdd(db_acc + ((long long)st.pixc * a.N + db_n), v);
             }
-            --st.pixc;
+            st.pixc -= a.dir;
         }
         if (++st.jc == W) { st.jc = 0; ++st.qc; }
     };

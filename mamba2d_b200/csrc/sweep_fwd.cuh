@@ -31,6 +31,7 @@ struct ScanArgs {
     const void *x, *dT, *dL, *AT, *AL, *BT, *BL, *C, *D;
     long long pBT, pBL, pC;   // pixel pitch (elements) of BT, BL, C
     void* y;
+    int dir;                  // +1: scan from the top-left corner; -1: from the bottom-right one (same memory, walked backwards)
     float4* ring;             // per-CTA band-boundary ring: [cta][W][4][32] float4
     int Rb, nbands;
     // ---- several CTAs per image (large maps, few images): CTA c of a chain of `chain` CTAs owns the
@@ -52,6 +53,13 @@ struct ScanArgs {
     void *d_x, *d_dT, *d_dL;
 };
 typedef ScanArgs FwdArgs;
+
+// Flat pixel index in memory of scan position (i, j) of image b.  In the reverse direction the
+// scan's cell (i, j) is the memory's pixel (H-1-i, W-1-j), i.e. the image's pixels in opposite order.
+__device__ __forceinline__ int scan_pixel(const ScanArgs& a, int b, int i, int j) {
+    const int p = i * a.W + j;
+    return b * a.H * a.W + (a.dir > 0 ? p : a.H * a.W - 1 - p);
+}
 
 // Shared-memory hand-off layout: [slot 0..warps][parity 0..1][4][32] float4.  Rank k reads slot k
 // and writes slot k+1; slot 0 receives the ring pull.
@@ -115,7 +123,7 @@ __device__ __forceinline__ int wait_columns(const int* counter, int need, int* s
 // pixel index (one multiply-add each); the host guarantees that every element index fits 31 bits.
 struct FwdRun {
     // ---- load side: the cell whose inputs are fetched next ----
-    int pixl;               // flat pixel index (b*H + i)*W + j
+    int pixl;               // flat pixel index in memory of the cell (see scan_pixel)
     int jl, ql, bil;
     bool row_l, pull_l;
     int seen;               // columns of the band above known to be published (chained CTAs)
@@ -198,7 +206,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
             const int b = img0 + st.bil * img_stride;
             st.row_l = (r < Rb) && (i < H);
             st.pull_l = st.row_l && (r == 0) && (q > 0);
-            st.pixl = (b * H + i) * W;
+            st.pixl = scan_pixel(a, b, i, 0);
             if (chain > 1 && q > 0) {   // the band above belongs to another CTA
                 const size_t band = ((size_t)b * groups + g) * nbands + (q - 1);
                 st.pull = a.bnd + band * W * kSlotF4 + lane;
@@ -232,7 +240,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                     }
                     // the row above lives in the previous band: pull it from the ring into slot 0
                     cp_async16x4_if(st.pull_l, smem_u32(my + (par * CB + cc) * kSlotF4), st.pull + col * kSlotF4);
-                    ++st.pixl;
+                    st.pixl += a.dir;
                 }
             }
         }
@@ -256,7 +264,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                 st.push = a.bnd + band * W * kSlotF4 + lane;
                 st.ccount = a.progress + band;
             }
-            st.pixc = (b * H + i) * W;
+            st.pixc = scan_pixel(a, b, i, 0);
             if (STORE_HS) st.phs = a.hs + (((size_t)b * groups + g) * H * W + (size_t)i * W) * HsBlock<io_t>::f4 + lane;
         }
         if (st.row_c) {
@@ -360,7 +368,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                         const float ysum = reduce_states(yacc[0], yacc[1], yacc[2], yacc[3], nq);
                         if (y_lane) store1(static_cast<io_t*>(a.y), st.pixc * E + g * kGroup + lane, fmaf(sel4(cur.x, nq), D_own, ysum));
                     }
-                    ++st.pixc;
+                    st.pixc += a.dir;
                 }
             }
             if (chain > 1 && st.push_c) {

@@ -4,10 +4,13 @@ captures and for one-off timings.
     python -m mamba2d_b200.profile_case --shape 128,56,56,64 [--dtype f32|bf16] [--bwd] [--iters 3]
     python -m mamba2d_b200.profile_case --sweep 64,128,256,512,1024 [--reference]
     python -m mamba2d_b200.profile_case --shape 2,200,336,64 --bwd --time [--reference]
+    python -m mamba2d_b200.profile_case --shape 128,56,56,64 --bwd --time --corner BR
 
 Inputs are seeded synthetic tensors (N = 16 states, BT/BL/C as strided views of one projection
 buffer).  ``--time`` prints CUDA-event timings; ``--reference`` also times the reference
 project's own CUDA extension when it has been prebuilt (oracle/_ref/), for comparison.
+``--corner BR`` times the scan from the bottom-right corner and, beside it, the reference's way
+of getting that direction: flip copies of every per-pixel tensor, the top-left scan, flip back.
 """
 import argparse
 import math
@@ -67,6 +70,23 @@ def reference_ext():
         return None
 
 
+def run_corner(B, H, W, E, dtype, bwd, iters):
+    """Native bottom-right scan against flip + top-left scan + flip at the level of the module:
+    the module flips x once on the way in and y once on the way out (and, in training, the
+    gradient on the way in and d_x on the way out)."""
+    from mamba2d_b200 import scan_bwd, scan_fwd
+    d = make_inputs(B, H, W, E, dtype=dtype)
+    a = [d[k] for k in ORDER]
+    native = timeit(lambda: scan_fwd(*a, reverse=True), iters)
+    flips = timeit(lambda: scan_fwd(d["x"].flip(1, 2), *a[1:]).flip(1, 2), iters)
+    line = f"B={B} {H}x{W} E={E} {str(dtype).split('.')[-1]} corner BR: fwd native {native:.3f} ms, flip+scan+flip {flips:.3f} ms"
+    if bwd:
+        native = timeit(lambda: scan_bwd(*a, d["gy"], reverse=True), iters)
+        flips = timeit(lambda: scan_bwd(*a, d["gy"].flip(1, 2))[0].flip(1, 2), iters)
+        line += f" | bwd native {native:.3f} ms, flip+scan+flip {flips:.3f} ms"
+    print(line, flush=True)
+
+
 def run_case(B, H, W, E, dtype, bwd, iters, timed, with_ref):
     from mamba2d_b200 import scan_bwd, scan_fwd
     d = make_inputs(B, H, W, E, dtype=dtype)
@@ -100,6 +120,7 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--reference", action="store_true")
+    ap.add_argument("--corner", choices=("TL", "BR"), default="TL")
     args = ap.parse_args()
     dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
     if args.sweep:
@@ -107,6 +128,9 @@ def main():
             run_case(1, hw, hw, 64, dtype, False, args.iters, True, args.reference and hw <= 1024)
         return
     B, H, W, E = (int(v) for v in args.shape.split(","))
+    if args.corner == "BR":
+        run_corner(B, H, W, E, dtype, args.bwd, max(args.iters, 10))
+        return
     run_case(B, H, W, E, dtype, args.bwd, args.iters, args.time, args.reference)
 
 

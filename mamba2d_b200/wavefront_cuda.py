@@ -12,6 +12,12 @@ copy under ``downstream/Mamba2D``) can import this module in its place unchanged
 What differs underneath: the reference launches one kernel per anti-diagonal, materialises the 5-D
 hidden state and finishes the readout and the gradient arithmetic in PyTorch.  Here the forward and
 the backward are one fused sm_100a kernel each, reached through the C ABI in ``include/m2d_scan.h``.
+One extension beyond the reference's signatures: every entry takes a trailing ``scan_start`` /
+``reverse`` argument (default: the reference's behaviour).  ``scan_start="BR"`` runs the scan from
+the bottom-right corner in place, which is what the reference's ``M2DBlock.forward`` obtains with
+two ``torch.flip`` copies around the block (models/mamba2d.py:162-175) and ``M2DBlock.ssm`` with a
+third one for ``double_scans`` (:190-200).
+
 There is no PyTorch or CPU fallback: tensors must live on a CUDA device and the prebuilt library
 must be present, otherwise a ``RuntimeError`` is raised.
 """
@@ -72,7 +78,7 @@ def _check_inputs(x, dT, dL, AT, AL, BT, BL, C, D, gy=None):
     return B, H, W, E, N
 
 
-def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D):
+def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D, reverse=False):
     B, H, W, E = x.shape
     N = AT.shape[1]
     keep = []   # tensors that must outlive the launch call
@@ -80,6 +86,7 @@ def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D):
     d.struct_bytes = ctypes.sizeof(_lib.ScanDesc)
     d.dtype = _DTYPES[x.dtype]
     d.B, d.H, d.W, d.E, d.N = B, H, W, E, N
+    d.flags = _lib.M2D_SCAN_REVERSE if reverse else 0
     for name, t in (("x", x), ("dT", dT), ("dL", dL), ("AT", AT), ("AL", AL), ("D", D)):
         t = t.contiguous()
         keep.append(t)
@@ -100,8 +107,11 @@ def _workspace(d, nbytes, device, keep):
         d.workspace_bytes = int(nbytes)
 
 
-def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D):
+def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
     """Fused forward: y (B,H,W,E) in ``x.dtype``.  Inputs as ``wf_cuda_fn_pr.apply`` takes them.
+
+    ``reverse=True`` scans from the bottom-right corner: the result equals
+    ``scan_fwd(*[t.flip(1, 2) for t in pixel_tensors], ...).flip(1, 2)`` without any copy.
 
     With few images on a large map the kernel runs several CTAs per image that wait on one another
     with bounded polling; set ``M2D_CHECK_STATUS=1`` to synchronise after the call and raise if
@@ -109,7 +119,7 @@ def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D):
     _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
     L = _lib.lib()
     with torch.cuda.device(x.device):
-        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         d.y = y.data_ptr()
         _workspace(d, L.m2d_scan_fwd_workspace(ctypes.byref(d)), x.device, keep)
@@ -122,14 +132,14 @@ def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D):
     return y
 
 
-def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output):
+def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False):
     """Fused backward with recomputation.  Returns the nine gradients
     (d_x, d_deltaT, d_deltaL, d_AT, d_AL, d_BT, d_BL, d_C, d_D), all in ``x.dtype``."""
     B, H, W, E, N = _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output)
     L = _lib.lib()
     dev, dt = x.device, x.dtype
     with torch.cuda.device(dev):
-        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
         gy = grad_output.contiguous()
         keep.append(gy)
         d.gy = gy.data_ptr()
@@ -157,24 +167,25 @@ def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output):
 
 @torch.library.custom_op("mamba2d_b200::scan_fwd", mutates_args=())
 def scan_fwd_op(x: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, AT: torch.Tensor, AL: torch.Tensor,
-                BT: torch.Tensor, BL: torch.Tensor, C: torch.Tensor, D: torch.Tensor) -> torch.Tensor:
-    return scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+                BT: torch.Tensor, BL: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
+                reverse: bool = False) -> torch.Tensor:
+    return scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
 
 
 @scan_fwd_op.register_fake
-def _scan_fwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D):
+def _scan_fwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
     return torch.empty_like(x, memory_format=torch.contiguous_format)
 
 
 @torch.library.custom_op("mamba2d_b200::scan_bwd", mutates_args=())
 def scan_bwd_op(x: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, AT: torch.Tensor, AL: torch.Tensor,
                 BT: torch.Tensor, BL: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
-                grad_output: torch.Tensor) -> list[torch.Tensor]:
-    return list(scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output))
+                grad_output: torch.Tensor, reverse: bool = False) -> list[torch.Tensor]:
+    return list(scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse))
 
 
 @scan_bwd_op.register_fake
-def _scan_bwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output):
+def _scan_bwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False):
     B, H, W, E = x.shape
     N = AT.shape[1]
     mk = lambda *s: x.new_empty(s)
@@ -214,16 +225,17 @@ class wf_cuda_fn_pr(torch.autograd.Function):
     recomputed inside the backward kernel."""
 
     @staticmethod
-    def forward(ctx, x, deltaT, deltaL, AT, AL, BT, BL, C, D):
-        y = scan_fwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+    def forward(ctx, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
+        y = scan_fwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
         ctx.save_for_backward(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        ctx.reverse = bool(reverse)
         return y
 
     @staticmethod
     def backward(ctx, grad_output):
         x, deltaT, deltaL, AT, AL, BT, BL, C, D = ctx.saved_tensors
-        grads = scan_bwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output.to(x.dtype))
-        return tuple(grads)
+        grads = scan_bwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output.to(x.dtype), ctx.reverse)
+        return (*grads, None)
 
 
 class wf_cuda_fn_fr(torch.autograd.Function):
@@ -231,11 +243,12 @@ class wf_cuda_fn_fr(torch.autograd.Function):
     an autograd graph) in backward, as in the reference."""
 
     @staticmethod
-    def forward(ctx, x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D):
+    def forward(ctx, x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, reverse=False):
         with torch.no_grad():
             deltaT, deltaL, AT, AL, BT, BL, C = proj_params(
                 x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
-        y = scan_fwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        y = scan_fwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+        ctx.reverse = bool(reverse)
         ctx.save_for_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D)
         return y
 
@@ -249,22 +262,29 @@ class wf_cuda_fn_fr(torch.autograd.Function):
             proj = proj_params(*leaves)
         deltaT, deltaL, AT, AL, BT, BL, C = (t.detach() for t in proj)
         d_x_scan, d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C, d_D = scan_bwd_op(
-            x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output)
+            x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, ctx.reverse)
         # proj returns (deltaT, deltaL, AT, AL, BT, BL, C)
         g = torch.autograd.grad(list(proj), leaves, [d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C], retain_graph=False)
         d_x = d_x_scan + g[0]
-        return (d_x, *g[1:], d_D)
+        return (d_x, *g[1:], d_D, None)
 
 
-def wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, recomp="partial"):
+def wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, recomp="partial",
+                        scan_start="TL"):
     """The op as ``M2DBlock.ssm`` calls it.
 
     Args:
         recomp: ``"partial"`` saves the projections for backward; ``"full"`` saves only x and the
             weights and recomputes the projections in backward (less memory, slower).
+        scan_start: ``"TL"`` (the reference's only direction) or ``"BR"``: scan from the bottom-right
+            corner, equal to ``wavefront_scan_cuda(x.flip(1, 2), ...).flip(1, 2)`` without the copies.
     Raises:
-        ValueError: if H < 2 or W < 2, or for an unknown ``recomp`` (same conditions as the reference).
+        ValueError: if H < 2 or W < 2, or for an unknown ``recomp`` (same conditions as the
+            reference) or ``scan_start``.
     """
+    if scan_start not in ("TL", "BR"):
+        raise ValueError(f"Unknown scan start corner, got {scan_start}...")
+    reverse = scan_start == "BR"
     _, H, W, _ = x.shape
     if H < 2 or W < 2:
         raise ValueError(f"Wavefront scan kernel requires spatial dims > 1. Got H={H}, W={W}.")
@@ -279,7 +299,7 @@ def wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_
     if recomp == "partial":
         deltaT, deltaL, AT, AL, BT, BL, C = proj_params(
             x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
-        return wf_cuda_fn_pr.apply(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+        return wf_cuda_fn_pr.apply(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
     if recomp == "full":
-        return wf_cuda_fn_fr.apply(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D)
+        return wf_cuda_fn_fr.apply(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, reverse)
     raise ValueError(f"Unknown recomputation mode, got {recomp}...")

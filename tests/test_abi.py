@@ -35,7 +35,7 @@ def test_every_declared_symbol_is_exported(L):
 def test_version_and_strerror(L):
     assert L.m2d_abi_version() == _lib.ABI_VERSION
     assert _lib.strerror(0) == "ok"
-    for code in range(-9, 0):
+    for code in range(-10, 0):
         assert _lib.strerror(code) not in ("ok", "unknown status")
     assert _lib.strerror(-99) == "unknown status"
 
@@ -60,6 +60,8 @@ def test_descriptor_validation_without_a_device(L):
     assert L.m2d_scan_fwd(ctypes.byref(_desc(dtype=7)), None) == -2
     assert L.m2d_scan_fwd(ctypes.byref(_desc(C_pitch=8)), None) == -5
     assert L.m2d_scan_fwd(ctypes.byref(_desc(struct_bytes=8)), None) == -8
+    assert L.m2d_scan_fwd(ctypes.byref(_desc(flags=2)), None) == -10   # unknown flag bit
+    assert L.m2d_scan_bwd(ctypes.byref(_desc(flags=_lib.M2D_SCAN_REVERSE)), None) == -1   # known bit: next check
     assert L.m2d_scan_fwd(None, None) == -1
 
 
