@@ -1,4 +1,4 @@
-"""ctypes binding of the C-ABI library (include/m2d_scan.h).
+"""ctypes binding of the C-ABI library (include/m2d_scan.h, include/m2d_proj.h).
 
 The library is prebuilt by ``python -m mamba2d_b200.build``.  There is no fallback: if the shared
 object is missing or a call fails, this module raises.
@@ -15,7 +15,9 @@ ABI_VERSION = 2
 NOALLOC_SCRATCH_BYTES = 32 << 20     # M2D_NOALLOC_SCRATCH_BYTES in include/m2d_scan.h
 
 EXPORTS = ("m2d_abi_version", "m2d_strerror", "m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace",
-           "m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc", "m2d_scan_fwd_status_offset", "m2d_scan_bwd_status_offset")
+           "m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc", "m2d_scan_fwd_status_offset", "m2d_scan_bwd_status_offset",
+           "m2d_proj_workspace", "m2d_dtproj_fwd", "m2d_dtproj_bwd", "m2d_xproj_wgrad")
+PROJ_MAX_E, PROJ_MAX_R = 640, 64     # M2D_PROJ_MAX_E / M2D_PROJ_MAX_R in include/m2d_proj.h
 
 
 class ScanDesc(ctypes.Structure):
@@ -33,6 +35,20 @@ class ScanDesc(ctypes.Structure):
         ("d_AT", ctypes.c_void_p), ("d_AL", ctypes.c_void_p),
         ("d_BT", ctypes.c_void_p), ("d_BL", ctypes.c_void_p), ("d_C", ctypes.c_void_p), ("d_D", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
+    ]
+
+
+class ProjDesc(ctypes.Structure):
+    """Mirror of ``m2d_proj_desc``."""
+    _fields_ = [
+        ("struct_bytes", ctypes.c_uint32), ("dtype", ctypes.c_int32), ("P", ctypes.c_int64),
+        ("E", ctypes.c_int32), ("R", ctypes.c_int32), ("N", ctypes.c_int32), ("reserved0", ctypes.c_int32),
+        ("proj_pitch", ctypes.c_int64),
+        ("x", ctypes.c_void_p), ("proj", ctypes.c_void_p), ("WT", ctypes.c_void_p), ("WL", ctypes.c_void_p),
+        ("bT", ctypes.c_void_p), ("bL", ctypes.c_void_p), ("dT", ctypes.c_void_p), ("dL", ctypes.c_void_p),
+        ("g_dT", ctypes.c_void_p), ("g_dL", ctypes.c_void_p), ("d_proj", ctypes.c_void_p),
+        ("d_WT", ctypes.c_void_p), ("d_WL", ctypes.c_void_p), ("d_bT", ctypes.c_void_p), ("d_bL", ctypes.c_void_p),
+        ("d_Wx", ctypes.c_void_p), ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
     ]
 
 
@@ -60,6 +76,11 @@ def lib():
         for name in ("m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc"):
             getattr(L, name).restype = ctypes.c_int
             getattr(L, name).argtypes = [ctypes.POINTER(ScanDesc), ctypes.c_void_p]
+        L.m2d_proj_workspace.restype = ctypes.c_uint64
+        L.m2d_proj_workspace.argtypes = [ctypes.POINTER(ProjDesc)]
+        for name in ("m2d_dtproj_fwd", "m2d_dtproj_bwd", "m2d_xproj_wgrad"):
+            getattr(L, name).restype = ctypes.c_int
+            getattr(L, name).argtypes = [ctypes.POINTER(ProjDesc), ctypes.c_void_p]
         if L.m2d_abi_version() != ABI_VERSION:
             raise RuntimeError(f"libm2d_scan.so has ABI {L.m2d_abi_version()}, expected {ABI_VERSION}")
         _LIB = L

@@ -5,12 +5,16 @@ captures and for one-off timings.
     python -m mamba2d_b200.profile_case --sweep 64,128,256,512,1024 [--reference]
     python -m mamba2d_b200.profile_case --shape 2,200,336,64 --bwd --time [--reference]
     python -m mamba2d_b200.profile_case --shape 128,56,56,64 --bwd --time --corner BR
+    python -m mamba2d_b200.profile_case --shape 128,56,56,64 --entry
 
 Inputs are seeded synthetic tensors (N = 16 states, BT/BL/C as strided views of one projection
 buffer).  ``--time`` prints CUDA-event timings; ``--reference`` also times the reference
 project's own CUDA extension when it has been prebuilt (oracle/_ref/), for comparison.
 ``--corner BR`` times the scan from the bottom-right corner and, beside it, the reference's way
 of getting that direction: flip copies of every per-pixel tensor, the top-left scan, flip back.
+``--entry`` times forward + backward of the module-level entry (projections included) in both
+recomputation modes, and the same with the projections in plain PyTorch under autograd (the
+reference's formulation) around the same scan kernels.
 """
 import argparse
 import math
@@ -87,6 +91,58 @@ def run_corner(B, H, W, E, dtype, bwd, iters):
     print(line, flush=True)
 
 
+def run_entry(B, H, W, E, dtype, iters):
+    """wavefront_scan_cuda forward + backward with module-shaped weights (A_log = log(1..N), dt_rank = E/16)."""
+    from mamba2d_b200 import wavefront_cuda as wc
+    N, R = 16, math.ceil(E / 16)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(B, H, W, E, generator=g).to("cuda", dtype).requires_grad_(True)
+    gy = torch.randn(B, H, W, E, generator=g).to("cuda", dtype)
+    A_log = torch.log(torch.arange(1, N + 1, dtype=torch.float32).repeat(E, 1)).cuda()
+    mk = lambda *s, scale: ((torch.rand(*s, generator=g) * 2 - 1) * scale).to("cuda", dtype).requires_grad_(True)
+    w = [A_log.clone().requires_grad_(True), A_log.clone().requires_grad_(True), mk(2 * R + 3 * N, E, scale=E ** -0.5),
+         mk(E, R, scale=R ** -0.5), mk(E, scale=1.0), mk(E, R, scale=R ** -0.5), mk(E, scale=1.0),
+         torch.ones(E, device="cuda", dtype=dtype, requires_grad=True)]
+
+    def torch_proj(x, AT_log, AL_log, wx, wT, bT, wL, bL):   # the reference's formulation, differentiated by autograd
+        p = F.linear(x, wx)
+        rT, rL, BT, BL, C = torch.split(p, [R, R, N, N, N], dim=-1)
+        return (F.softplus(F.linear(rT, wT, bT)), F.softplus(F.linear(rL, wL, bL)),
+                (-torch.exp(AT_log.float())).to(x.dtype), (-torch.exp(AL_log.float())).to(x.dtype), BT, BL, C)
+
+    class autograd_full(torch.autograd.Function):   # the reference's structure: graph + autograd.grad in backward
+        @staticmethod
+        def forward(ctx, x, *w):
+            with torch.no_grad():
+                p = torch_proj(x, *w[:7])
+            ctx.save_for_backward(x, *w)
+            return wc.scan_fwd_op(x, *p, w[7])
+
+        @staticmethod
+        def backward(ctx, gy):
+            x, *w = ctx.saved_tensors
+            with torch.enable_grad():
+                leaves = [t.detach().requires_grad_(True) for t in (x, *w[:7])]
+                proj = torch_proj(*leaves)
+            p = [t.detach() for t in proj]
+            gs = wc.scan_bwd_op(x, *p, w[7], gy)
+            g = torch.autograd.grad(list(proj), leaves, [gs[1], gs[2], gs[3], gs[4], gs[5], gs[6], gs[7]])
+            return (gs[0] + g[0], *g[1:], gs[8])
+
+    def step(fn):
+        for t in [x] + w:
+            t.grad = None
+        fn().backward(gy)
+
+    line = f"B={B} {H}x{W} E={E} {str(dtype).split('.')[-1]} entry fwd+bwd:"
+    for name, fn in (("partial", lambda: wc.wavefront_scan_cuda(x, *w, "partial")),
+                     ("full", lambda: wc.wavefront_scan_cuda(x, *w, "full")),
+                     ("partial, projections in PyTorch", lambda: wc.wf_cuda_fn_pr.apply(x, *torch_proj(x, *w[:7]), w[7])),
+                     ("full, projections in PyTorch", lambda: autograd_full.apply(x, *w))):
+        line += f" {name} {timeit(lambda: step(fn), iters):.3f} ms,"
+    print(line.rstrip(","), flush=True)
+
+
 def run_case(B, H, W, E, dtype, bwd, iters, timed, with_ref):
     from mamba2d_b200 import scan_bwd, scan_fwd
     d = make_inputs(B, H, W, E, dtype=dtype)
@@ -121,6 +177,7 @@ def main():
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--reference", action="store_true")
     ap.add_argument("--corner", choices=("TL", "BR"), default="TL")
+    ap.add_argument("--entry", action="store_true")
     args = ap.parse_args()
     dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
     if args.sweep:
@@ -128,6 +185,9 @@ def main():
             run_case(1, hw, hw, 64, dtype, False, args.iters, True, args.reference and hw <= 1024)
         return
     B, H, W, E = (int(v) for v in args.shape.split(","))
+    if args.entry:
+        run_entry(B, H, W, E, dtype, max(args.iters, 10))
+        return
     if args.corner == "BR":
         run_corner(B, H, W, E, dtype, args.bwd, max(args.iters, 10))
         return

@@ -194,26 +194,190 @@ def _scan_bwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse
 
 
 # -----------------------------------------------------------------------------
-# Projections (plain PyTorch on both sides of the comparison; cuBLAS GEMMs)
+# Projections.  The x projection and its data gradient are GEMMs and stay on the GEMM library; the
+# rank-R dt projections with their softplus, their backward, and the weight gradient of the x
+# projection (reductions over every pixel into a tiny matrix) are fused kernels of this library
+# (include/m2d_proj.h).  CPU tensors and shapes outside the kernels' range take the plain PyTorch
+# formulation, which is what the reference runs everywhere (wavefront_cuda.py:63-95).
 # -----------------------------------------------------------------------------
+
+def _proj_desc(proj, E, R, N):
+    d = _lib.ProjDesc()
+    d.struct_bytes = ctypes.sizeof(_lib.ProjDesc)
+    d.dtype = _DTYPES[proj.dtype]
+    d.P = proj.numel() // proj.shape[-1]
+    d.E, d.R, d.N = E, R, N
+    d.proj_pitch = proj.shape[-1]
+    return d
+
+
+def _proj_call(fn_name, d, device, keep):
+    L = _lib.lib()
+    with torch.cuda.device(device):
+        _workspace(d, L.m2d_proj_workspace(ctypes.byref(d)), device, keep)
+        rc = getattr(L, fn_name)(ctypes.byref(d), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(rc, fn_name)
+
+
+def _fusable(x, proj_cols, R):
+    """The fused projection kernels cover CUDA tensors in fp32 / bf16 with E <= 640, a dt rank of at
+    most 64 and (rounded up to a power of two) at most a quarter of the channels, and channel
+    counts / row pitches that are multiples of 4 (every shipped model)."""
+    E = x.shape[-1]
+    rank_bucket = next((b for b in (4, 8, 16, 32, 64) if R <= b), None)
+    return (x.is_cuda and x.dtype in _DTYPES and E <= _lib.PROJ_MAX_E and rank_bucket is not None
+            and 4 * rank_bucket <= (E + 31) // 32 * 32 and E % 4 == 0 and proj_cols % 4 == 0)
+
+
+@torch.library.custom_op("mamba2d_b200::dtproj_fwd", mutates_args=())
+def dtproj_fwd_op(proj: torch.Tensor, WT: torch.Tensor, bT: torch.Tensor, WL: torch.Tensor, bL: torch.Tensor,
+                  d_state: int) -> list[torch.Tensor]:
+    """deltaT, deltaL = softplus(proj[..., :R] @ WT^T + bT), softplus(proj[..., R:2R] @ WL^T + bL)."""
+    E, R = WT.shape
+    proj = proj.contiguous()
+    keep = [t.contiguous() for t in (WT, WL, bT, bL)]
+    d = _proj_desc(proj, E, R, d_state)
+    d.proj = proj.data_ptr()
+    d.WT, d.WL, d.bT, d.bL = (t.data_ptr() for t in keep)
+    dT = torch.empty(proj.shape[:-1] + (E,), dtype=proj.dtype, device=proj.device)
+    dL = torch.empty_like(dT)
+    d.dT, d.dL = dT.data_ptr(), dL.data_ptr()
+    _proj_call("m2d_dtproj_fwd", d, proj.device, keep)
+    return [dT, dL]
+
+
+@dtproj_fwd_op.register_fake
+def _dtproj_fwd_fake(proj, WT, bT, WL, bL, d_state):
+    shape = proj.shape[:-1] + (WT.shape[0],)
+    return [proj.new_empty(shape), proj.new_empty(shape)]
+
+
+@torch.library.custom_op("mamba2d_b200::dtproj_bwd", mutates_args=("d_proj",))
+def dtproj_bwd_op(g_dT: torch.Tensor, g_dL: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, proj: torch.Tensor,
+                  WT: torch.Tensor, WL: torch.Tensor, d_proj: torch.Tensor, d_state: int) -> list[torch.Tensor]:
+    """Backward of dtproj_fwd.  Writes columns [0, 2R) of ``d_proj`` in place and returns
+    [d_WT, d_bT, d_WL, d_bL]."""
+    E, R = WT.shape
+    keep = [t.contiguous() for t in (g_dT, g_dL, deltaT, deltaL, proj, WT, WL)]
+    if not d_proj.is_contiguous():
+        raise RuntimeError("dtproj_bwd: d_proj must be contiguous")
+    d = _proj_desc(keep[4], E, R, d_state)
+    d.g_dT, d.g_dL, d.dT, d.dL, d.proj, d.WT, d.WL = (t.data_ptr() for t in keep)
+    d.d_proj = d_proj.data_ptr()
+    outs = [torch.empty_like(keep[5]), torch.empty(E, dtype=proj.dtype, device=proj.device),
+            torch.empty_like(keep[6]), torch.empty(E, dtype=proj.dtype, device=proj.device)]
+    d.d_WT, d.d_bT, d.d_WL, d.d_bL = (t.data_ptr() for t in outs)
+    _proj_call("m2d_dtproj_bwd", d, proj.device, keep)
+    return outs
+
+
+@dtproj_bwd_op.register_fake
+def _dtproj_bwd_fake(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, d_proj, d_state):
+    E = WT.shape[0]
+    return [torch.empty_like(WT), WT.new_empty(E), torch.empty_like(WL), WL.new_empty(E)]
+
+
+@torch.library.custom_op("mamba2d_b200::xproj_wgrad", mutates_args=())
+def xproj_wgrad_op(d_proj: torch.Tensor, x: torch.Tensor, d_state: int, dt_rank: int) -> torch.Tensor:
+    """d_Wx = d_proj^T @ x over all pixels: (2R+3N, E)."""
+    E = x.shape[-1]
+    keep = [d_proj.contiguous(), x.contiguous()]
+    d = _proj_desc(keep[0], E, dt_rank, d_state)
+    d.d_proj, d.x = keep[0].data_ptr(), keep[1].data_ptr()
+    out = torch.empty(2 * dt_rank + 3 * d_state, E, dtype=x.dtype, device=x.device)
+    d.d_Wx = out.data_ptr()
+    _proj_call("m2d_xproj_wgrad", d, x.device, keep)
+    return out
+
+
+@xproj_wgrad_op.register_fake
+def _xproj_wgrad_fake(d_proj, x, d_state, dt_rank):
+    return x.new_empty(2 * dt_rank + 3 * d_state, x.shape[-1])
+
+
+def _proj_forward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
+    """``proj_params`` without an autograd graph.  Returns the seven outputs and what the
+    hand-written backward needs: (proj, AT32, AL32) -- softplus' is recovered from deltaT / deltaL
+    themselves, so the pre-activations are not kept."""
+    d_state, dt_rank, dt = AT_log.shape[1], dt_projT_w.shape[1], x.dtype
+    AT32 = -torch.exp(AT_log.float())
+    AL32 = -torch.exp(AL_log.float())
+    proj = F.linear(x, x_proj_w)
+    rT, rL, BT, BL, C = torch.split(proj, [dt_rank, dt_rank, d_state, d_state, d_state], dim=-1)
+    if _fusable(x, proj.shape[-1], dt_rank):
+        deltaT, deltaL = dtproj_fwd_op(proj, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, d_state)
+    else:
+        deltaT = F.softplus(F.linear(rT, dt_projT_w, dt_projT_b))
+        deltaL = F.softplus(F.linear(rL, dt_projL_w, dt_projL_b))
+    out = (deltaT.to(dtype=dt), deltaL.to(dtype=dt), AT32.to(dtype=dt), AL32.to(dtype=dt),
+           BT.to(dtype=dt), BL.to(dtype=dt), C.to(dtype=dt))
+    return out, (proj, AT32, AL32)
+
+
+def _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, deltaL, saved,
+                   d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C):
+    """Gradients of ``proj_params`` (wavefront_cuda.py:63-95 in the reference) written out by hand:
+    softplus', the two dt projections, the x projection and the ``-exp(A_log)`` transform.  A
+    missing (None) upstream gradient counts as zero.
+    Returns (d_x, d_AT_log, d_AL_log, d_x_proj_w, d_dt_projT_w, d_dt_projT_b, d_dt_projL_w, d_dt_projL_b)."""
+    proj, AT32, AL32 = saved
+    E, R, N = x.shape[-1], dt_projT_w.shape[1], AT_log.shape[1]
+    dt = x.dtype
+    zeros_like_delta = lambda: torch.zeros_like(deltaT)
+    d_dT = zeros_like_delta() if d_dT is None else d_dT.to(dt)
+    d_dL = zeros_like_delta() if d_dL is None else d_dL.to(dt)
+    d_proj = torch.empty_like(proj, memory_format=torch.contiguous_format)
+    for k, g in enumerate((d_BT, d_BL, d_C)):
+        dst = d_proj[..., 2 * R + k * N:2 * R + (k + 1) * N]
+        if g is None:
+            dst.zero_()
+        else:
+            dst.copy_(g)
+    if _fusable(x, proj.shape[-1], R):
+        d_wT, d_bT, d_wL, d_bL = dtproj_bwd_op(d_dT, d_dL, deltaT, deltaL, proj, dt_projT_w, dt_projL_w, d_proj, N)
+        d_wx = xproj_wgrad_op(d_proj, x, N, R)
+    else:
+        # softplus'(z) = 1 - exp(-softplus(z)); values past the threshold of 20 give exactly 1
+        sT = d_dT * (-torch.expm1(-deltaT.float())).to(dt)
+        sL = d_dL * (-torch.expm1(-deltaL.float())).to(dt)
+        rT, rL = proj[..., :R], proj[..., R:2 * R]
+        d_wT = sT.reshape(-1, E).t() @ rT.reshape(-1, R)
+        d_wL = sL.reshape(-1, E).t() @ rL.reshape(-1, R)
+        d_bT, d_bL = sT.reshape(-1, E).sum(0), sL.reshape(-1, E).sum(0)
+        d_proj[..., :R] = sT @ dt_projT_w
+        d_proj[..., R:2 * R] = sL @ dt_projL_w
+        d_wx = d_proj.reshape(-1, d_proj.shape[-1]).t() @ x.reshape(-1, E)
+    d_x = d_proj @ x_proj_w
+    d_AT_log = None if d_AT is None else (d_AT.float() * AT32).to(AT_log.dtype)      # d(-exp(a))/da = -exp(a) = A
+    d_AL_log = None if d_AL is None else (d_AL.float() * AL32).to(AL_log.dtype)
+    return d_x, d_AT_log, d_AL_log, d_wx, d_wT, d_bT, d_wL, d_bL
+
+
+class _proj_params_fn(torch.autograd.Function):
+    """``proj_params`` as one autograd node with the hand-written backward."""
+
+    @staticmethod
+    def forward(ctx, x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
+        out, saved = _proj_forward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
+        ctx.save_for_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, out[0], out[1], *saved)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C):
+        x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, deltaL, proj, AT32, AL32 = ctx.saved_tensors
+        g = _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, deltaL, (proj, AT32, AL32),
+                           d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C)
+        d_x, d_AT_log, d_AL_log, d_wx, d_wT, d_bT, d_wL, d_bL = g
+        return d_x, d_AT_log, d_AL_log, d_wx, d_wT, d_bT, d_wL, d_bL
+
 
 def proj_params(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
     """Input-dependent scan parameters from x (B,H,W,E).
 
     Returns deltaT, deltaL (B,H,W,E), AT, AL (E,N), BT, BL, C (B,H,W,N), all in ``x.dtype``;
-    BT/BL/C are views into the x-projection output (pixel pitch 2R+3N), which the kernels read
-    in place."""
-    d_state = AT_log.shape[1]
-    dt_rank = dt_projT_w.shape[1]
-    AT = -torch.exp(AT_log.float())
-    AL = -torch.exp(AL_log.float())
-    delta2BC = F.linear(x, x_proj_w)
-    rT, rL, BT, BL, C = torch.split(delta2BC, [dt_rank, dt_rank, d_state, d_state, d_state], dim=-1)
-    deltaT = F.softplus(F.linear(rT, dt_projT_w, dt_projT_b))
-    deltaL = F.softplus(F.linear(rL, dt_projL_w, dt_projL_b))
-    dt = x.dtype
-    return (deltaT.to(dtype=dt), deltaL.to(dtype=dt), AT.to(dtype=dt), AL.to(dtype=dt),
-            BT.to(dtype=dt), BL.to(dtype=dt), C.to(dtype=dt))
+    BT/BL/C are views into the x-projection output (pixel pitch 2R+3N), which the scan kernels
+    read in place.  Differentiable: one autograd node whose backward is written by hand."""
+    return _proj_params_fn.apply(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
 
 
 # -----------------------------------------------------------------------------
@@ -239,13 +403,14 @@ class wf_cuda_fn_pr(torch.autograd.Function):
 
 
 class wf_cuda_fn_fr(torch.autograd.Function):
-    """Full recomputation: only x and the weights are saved; the projections are recomputed (with
-    an autograd graph) in backward, as in the reference."""
+    """Full recomputation: only x and the weights are saved; the projections are recomputed in
+    backward.  The reference recomputes them under autograd and calls ``torch.autograd.grad``
+    (wavefront_cuda.py:235-302); here their backward is written out (``_proj_backward``)."""
 
     @staticmethod
     def forward(ctx, x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, reverse=False):
         with torch.no_grad():
-            deltaT, deltaL, AT, AL, BT, BL, C = proj_params(
+            (deltaT, deltaL, AT, AL, BT, BL, C), _ = _proj_forward(
                 x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
         y = scan_fwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
         ctx.reverse = bool(reverse)
@@ -256,15 +421,13 @@ class wf_cuda_fn_fr(torch.autograd.Function):
     def backward(ctx, grad_output):
         x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D = ctx.saved_tensors
         grad_output = grad_output.to(x.dtype)
-        with torch.enable_grad():
-            leaves = [t.detach().requires_grad_(True) for t in
-                      (x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)]
-            proj = proj_params(*leaves)
-        deltaT, deltaL, AT, AL, BT, BL, C = (t.detach() for t in proj)
-        d_x_scan, d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C, d_D = scan_bwd_op(
-            x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, ctx.reverse)
-        # proj returns (deltaT, deltaL, AT, AL, BT, BL, C)
-        g = torch.autograd.grad(list(proj), leaves, [d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C], retain_graph=False)
+        with torch.no_grad():
+            (deltaT, deltaL, AT, AL, BT, BL, C), saved = _proj_forward(
+                x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
+            d_x_scan, d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C, d_D = scan_bwd_op(
+                x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, ctx.reverse)
+            g = _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, deltaL, saved,
+                               d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C)
         d_x = d_x_scan + g[0]
         return (d_x, *g[1:], d_D, None)
 

@@ -1,4 +1,4 @@
-"""The C-ABI library loads without a GPU and exports every symbol include/m2d_scan.h declares;
+"""The C-ABI library loads without a GPU and exports every symbol the headers under include/ declare;
 argument validation and launch planning run on the host."""
 import ctypes
 import os
@@ -19,7 +19,8 @@ def L():
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "m2d_scan.h")).read()
+    inc = os.path.join(ROOT, "include")
+    text = "".join(open(os.path.join(inc, f)).read() for f in sorted(os.listdir(inc)) if f.endswith(".h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(m2d_[a-z0-9_]+)\s*\(", text)))
 
@@ -90,3 +91,27 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.lib()
+
+
+def _pdesc(**kw):
+    d = _lib.ProjDesc()
+    d.struct_bytes = ctypes.sizeof(_lib.ProjDesc)
+    d.dtype = _lib.M2D_F32
+    d.P, d.E, d.R, d.N = 1000, 64, 4, 16
+    d.proj_pitch = 56
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+def test_projection_descriptor_validation_without_a_device(L):
+    assert L.m2d_dtproj_fwd(ctypes.byref(_pdesc()), None) == -1                  # NULL pointers
+    assert L.m2d_dtproj_bwd(ctypes.byref(_pdesc(struct_bytes=8)), None) == -8
+    assert L.m2d_dtproj_fwd(ctypes.byref(_pdesc(dtype=5)), None) == -2
+    assert L.m2d_dtproj_fwd(ctypes.byref(_pdesc(P=0)), None) == -3
+    assert L.m2d_dtproj_fwd(ctypes.byref(_pdesc(E=_lib.PROJ_MAX_E + 4)), None) == -9
+    assert L.m2d_dtproj_bwd(ctypes.byref(_pdesc(R=_lib.PROJ_MAX_R + 1, proj_pitch=400)), None) == -9
+    assert L.m2d_xproj_wgrad(ctypes.byref(_pdesc(proj_pitch=55)), None) == -5     # narrower than 2R+3N
+    ws = L.m2d_proj_workspace(ctypes.byref(_pdesc()))
+    assert ws > 0 and ws % 256 == 0
+    assert L.m2d_proj_workspace(ctypes.byref(_pdesc(R=0))) == 0                   # invalid descriptor

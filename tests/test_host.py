@@ -74,3 +74,31 @@ def test_proj_params_equals_restatement_on_cpu():
     for u, v in zip(a, b):
         assert torch.equal(u, v)
     assert not a[4].is_contiguous()     # BT stays a view into the projection output
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 2e-6), (torch.bfloat16, 2e-2)])
+def test_hand_written_projection_backward_equals_autograd(dt, tol):
+    """proj_params is one autograd node with a hand-written backward; autograd through the plain
+    PyTorch formulation (what the reference does, wavefront_cuda.py:63-95 and :235-302) is the
+    check.  CPU tensors take the PyTorch branch of that backward."""
+    E, N = 48, 16
+    p = inputs.make_module_params(E, N, seed=2)
+    names = ("AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w", "dt_projL_b")
+    w = {k: (v if k.endswith("_log") else v.to(dt)) for k, v in p.items()}
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(2, 5, 4, E, generator=g).to(dt)
+
+    def grads(fn):
+        leaves = [x.clone().requires_grad_(True)] + [w[k].clone().requires_grad_(True) for k in names]
+        out = fn(*leaves)
+        gg = torch.Generator().manual_seed(4)
+        gs = [torch.randn(o.shape, generator=gg).to(o.dtype) for o in out]
+        return [o.detach() for o in out], torch.autograd.grad(list(out), leaves, gs)
+
+    out_a, want = grads(torch_ref.proj_params_ref)
+    out_b, got = grads(wc.proj_params)
+    for a, b in zip(out_a, out_b):
+        assert torch.equal(a, b)
+    for name, a, b in zip(("x",) + names, want, got):
+        assert a.dtype == b.dtype and a.shape == b.shape, name
+        assert (a.float() - b.float()).abs().max() <= tol * a.float().abs().max(), name
