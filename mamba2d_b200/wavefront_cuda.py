@@ -165,6 +165,16 @@ def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False
 # wavefront_cuda.py:25-57)
 # -----------------------------------------------------------------------------
 
+_EAGER = {}     # operator -> its Python body
+
+
+def _run(op, *args):
+    """The registered operator while a compiler is tracing (it needs the opaque op and its fake);
+    the operator's Python body directly in eager mode, where the dispatcher round trip of a custom
+    operator costs more than the small stages' kernels."""
+    return op(*args) if torch.compiler.is_compiling() else _EAGER[op](*args)
+
+
 @torch.library.custom_op("mamba2d_b200::scan_fwd", mutates_args=())
 def scan_fwd_op(x: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, AT: torch.Tensor, AL: torch.Tensor,
                 BT: torch.Tensor, BL: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
@@ -229,9 +239,7 @@ def _fusable(x, proj_cols, R):
             and 4 * rank_bucket <= (E + 31) // 32 * 32 and E % 4 == 0 and proj_cols % 4 == 0)
 
 
-@torch.library.custom_op("mamba2d_b200::dtproj_fwd", mutates_args=())
-def dtproj_fwd_op(proj: torch.Tensor, WT: torch.Tensor, bT: torch.Tensor, WL: torch.Tensor, bL: torch.Tensor,
-                  d_state: int) -> list[torch.Tensor]:
+def _dtproj_fwd(proj, WT, bT, WL, bL, d_state):
     """deltaT, deltaL = softplus(proj[..., :R] @ WT^T + bT), softplus(proj[..., R:2R] @ WL^T + bL)."""
     E, R = WT.shape
     proj = proj.contiguous()
@@ -246,15 +254,19 @@ def dtproj_fwd_op(proj: torch.Tensor, WT: torch.Tensor, bT: torch.Tensor, WL: to
     return [dT, dL]
 
 
+@torch.library.custom_op("mamba2d_b200::dtproj_fwd", mutates_args=())
+def dtproj_fwd_op(proj: torch.Tensor, WT: torch.Tensor, bT: torch.Tensor, WL: torch.Tensor, bL: torch.Tensor,
+                  d_state: int) -> list[torch.Tensor]:
+    return _dtproj_fwd(proj, WT, bT, WL, bL, d_state)
+
+
 @dtproj_fwd_op.register_fake
 def _dtproj_fwd_fake(proj, WT, bT, WL, bL, d_state):
     shape = proj.shape[:-1] + (WT.shape[0],)
     return [proj.new_empty(shape), proj.new_empty(shape)]
 
 
-@torch.library.custom_op("mamba2d_b200::dtproj_bwd", mutates_args=("d_proj",))
-def dtproj_bwd_op(g_dT: torch.Tensor, g_dL: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, proj: torch.Tensor,
-                  WT: torch.Tensor, WL: torch.Tensor, d_proj: torch.Tensor, d_state: int) -> list[torch.Tensor]:
+def _dtproj_bwd(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, d_proj, d_state):
     """Backward of dtproj_fwd.  Writes columns [0, 2R) of ``d_proj`` in place and returns
     [d_WT, d_bT, d_WL, d_bL]."""
     E, R = WT.shape
@@ -271,14 +283,19 @@ def dtproj_bwd_op(g_dT: torch.Tensor, g_dL: torch.Tensor, deltaT: torch.Tensor, 
     return outs
 
 
+@torch.library.custom_op("mamba2d_b200::dtproj_bwd", mutates_args=("d_proj",))
+def dtproj_bwd_op(g_dT: torch.Tensor, g_dL: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, proj: torch.Tensor,
+                  WT: torch.Tensor, WL: torch.Tensor, d_proj: torch.Tensor, d_state: int) -> list[torch.Tensor]:
+    return _dtproj_bwd(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, d_proj, d_state)
+
+
 @dtproj_bwd_op.register_fake
 def _dtproj_bwd_fake(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, d_proj, d_state):
     E = WT.shape[0]
     return [torch.empty_like(WT), WT.new_empty(E), torch.empty_like(WL), WL.new_empty(E)]
 
 
-@torch.library.custom_op("mamba2d_b200::xproj_wgrad", mutates_args=())
-def xproj_wgrad_op(d_proj: torch.Tensor, x: torch.Tensor, d_state: int, dt_rank: int) -> torch.Tensor:
+def _xproj_wgrad(d_proj, x, d_state, dt_rank):
     """d_Wx = d_proj^T @ x over all pixels: (2R+3N, E)."""
     E = x.shape[-1]
     keep = [d_proj.contiguous(), x.contiguous()]
@@ -290,9 +307,18 @@ def xproj_wgrad_op(d_proj: torch.Tensor, x: torch.Tensor, d_state: int, dt_rank:
     return out
 
 
+@torch.library.custom_op("mamba2d_b200::xproj_wgrad", mutates_args=())
+def xproj_wgrad_op(d_proj: torch.Tensor, x: torch.Tensor, d_state: int, dt_rank: int) -> torch.Tensor:
+    return _xproj_wgrad(d_proj, x, d_state, dt_rank)
+
+
 @xproj_wgrad_op.register_fake
 def _xproj_wgrad_fake(d_proj, x, d_state, dt_rank):
     return x.new_empty(2 * dt_rank + 3 * d_state, x.shape[-1])
+
+
+_EAGER.update({scan_fwd_op: scan_fwd, scan_bwd_op: lambda *a: list(scan_bwd(*a)), dtproj_fwd_op: _dtproj_fwd,
+               dtproj_bwd_op: _dtproj_bwd, xproj_wgrad_op: _xproj_wgrad})
 
 
 def _proj_forward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
@@ -305,7 +331,7 @@ def _proj_forward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_
     proj = F.linear(x, x_proj_w)
     rT, rL, BT, BL, C = torch.split(proj, [dt_rank, dt_rank, d_state, d_state, d_state], dim=-1)
     if _fusable(x, proj.shape[-1], dt_rank):
-        deltaT, deltaL = dtproj_fwd_op(proj, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, d_state)
+        deltaT, deltaL = _run(dtproj_fwd_op, proj, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, d_state)
     else:
         deltaT = F.softplus(F.linear(rT, dt_projT_w, dt_projT_b))
         deltaL = F.softplus(F.linear(rL, dt_projL_w, dt_projL_b))
@@ -334,8 +360,8 @@ def _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, 
         else:
             dst.copy_(g)
     if _fusable(x, proj.shape[-1], R):
-        d_wT, d_bT, d_wL, d_bL = dtproj_bwd_op(d_dT, d_dL, deltaT, deltaL, proj, dt_projT_w, dt_projL_w, d_proj, N)
-        d_wx = xproj_wgrad_op(d_proj, x, N, R)
+        d_wT, d_bT, d_wL, d_bL = _run(dtproj_bwd_op, d_dT, d_dL, deltaT, deltaL, proj, dt_projT_w, dt_projL_w, d_proj, N)
+        d_wx = _run(xproj_wgrad_op, d_proj, x, N, R)
     else:
         # softplus'(z) = 1 - exp(-softplus(z)); values past the threshold of 20 give exactly 1
         sT = d_dT * (-torch.expm1(-deltaT.float())).to(dt)
@@ -390,7 +416,7 @@ class wf_cuda_fn_pr(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
-        y = scan_fwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+        y = _run(scan_fwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
         ctx.save_for_backward(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
         ctx.reverse = bool(reverse)
         return y
@@ -398,7 +424,7 @@ class wf_cuda_fn_pr(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         x, deltaT, deltaL, AT, AL, BT, BL, C, D = ctx.saved_tensors
-        grads = scan_bwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output.to(x.dtype), ctx.reverse)
+        grads = _run(scan_bwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output.to(x.dtype), ctx.reverse)
         return (*grads, None)
 
 
@@ -412,7 +438,7 @@ class wf_cuda_fn_fr(torch.autograd.Function):
         with torch.no_grad():
             (deltaT, deltaL, AT, AL, BT, BL, C), _ = _proj_forward(
                 x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
-        y = scan_fwd_op(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+        y = _run(scan_fwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
         ctx.reverse = bool(reverse)
         ctx.save_for_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D)
         return y
@@ -424,7 +450,7 @@ class wf_cuda_fn_fr(torch.autograd.Function):
         with torch.no_grad():
             (deltaT, deltaL, AT, AL, BT, BL, C), saved = _proj_forward(
                 x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
-            d_x_scan, d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C, d_D = scan_bwd_op(
+            d_x_scan, d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C, d_D = _run(scan_bwd_op, 
                 x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, ctx.reverse)
             g = _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, deltaL, saved,
                                d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C)
