@@ -266,33 +266,38 @@ def _dtproj_fwd_fake(proj, WT, bT, WL, bL, d_state):
     return [proj.new_empty(shape), proj.new_empty(shape)]
 
 
-def _dtproj_bwd(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, d_proj, d_state):
-    """Backward of dtproj_fwd.  Writes columns [0, 2R) of ``d_proj`` in place and returns
-    [d_WT, d_bT, d_WL, d_bL]."""
+def _dtproj_bwd(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, g_BT, g_BL, g_C):
+    """Backward of dtproj_fwd.  Returns [d_proj, d_WT, d_bT, d_WL, d_bL]: ``d_proj`` is the whole
+    gradient of the x-projection output -- columns [0, 2R) from the kernel, the rest copied from the
+    upstream gradients of BT, BL, C."""
     E, R = WT.shape
+    N = g_BT.shape[-1]
     keep = [t.contiguous() for t in (g_dT, g_dL, deltaT, deltaL, proj, WT, WL)]
-    if not d_proj.is_contiguous():
-        raise RuntimeError("dtproj_bwd: d_proj must be contiguous")
-    d = _proj_desc(keep[4], E, R, d_state)
+    d_proj = torch.empty_like(keep[4])
+    for k, g in enumerate((g_BT, g_BL, g_C)):
+        d_proj[..., 2 * R + k * N:2 * R + (k + 1) * N].copy_(g)
+    d = _proj_desc(keep[4], E, R, N)
     d.g_dT, d.g_dL, d.dT, d.dL, d.proj, d.WT, d.WL = (t.data_ptr() for t in keep)
     d.d_proj = d_proj.data_ptr()
-    outs = [torch.empty_like(keep[5]), torch.empty(E, dtype=proj.dtype, device=proj.device),
+    outs = [d_proj, torch.empty_like(keep[5]), torch.empty(E, dtype=proj.dtype, device=proj.device),
             torch.empty_like(keep[6]), torch.empty(E, dtype=proj.dtype, device=proj.device)]
-    d.d_WT, d.d_bT, d.d_WL, d.d_bL = (t.data_ptr() for t in outs)
+    d.d_WT, d.d_bT, d.d_WL, d.d_bL = (t.data_ptr() for t in outs[1:])
     _proj_call("m2d_dtproj_bwd", d, proj.device, keep)
     return outs
 
 
-@torch.library.custom_op("mamba2d_b200::dtproj_bwd", mutates_args=("d_proj",))
+@torch.library.custom_op("mamba2d_b200::dtproj_bwd", mutates_args=())
 def dtproj_bwd_op(g_dT: torch.Tensor, g_dL: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, proj: torch.Tensor,
-                  WT: torch.Tensor, WL: torch.Tensor, d_proj: torch.Tensor, d_state: int) -> list[torch.Tensor]:
-    return _dtproj_bwd(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, d_proj, d_state)
+                  WT: torch.Tensor, WL: torch.Tensor, g_BT: torch.Tensor, g_BL: torch.Tensor,
+                  g_C: torch.Tensor) -> list[torch.Tensor]:
+    return _dtproj_bwd(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, g_BT, g_BL, g_C)
 
 
 @dtproj_bwd_op.register_fake
-def _dtproj_bwd_fake(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, d_proj, d_state):
+def _dtproj_bwd_fake(g_dT, g_dL, deltaT, deltaL, proj, WT, WL, g_BT, g_BL, g_C):
     E = WT.shape[0]
-    return [torch.empty_like(WT), WT.new_empty(E), torch.empty_like(WL), WL.new_empty(E)]
+    return [torch.empty_like(proj, memory_format=torch.contiguous_format), torch.empty_like(WT), WT.new_empty(E),
+            torch.empty_like(WL), WL.new_empty(E)]
 
 
 def _xproj_wgrad(d_proj, x, d_state, dt_rank):
@@ -352,26 +357,21 @@ def _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, 
     zeros_like_delta = lambda: torch.zeros_like(deltaT)
     d_dT = zeros_like_delta() if d_dT is None else d_dT.to(dt)
     d_dL = zeros_like_delta() if d_dL is None else d_dL.to(dt)
-    d_proj = torch.empty_like(proj, memory_format=torch.contiguous_format)
-    for k, g in enumerate((d_BT, d_BL, d_C)):
-        dst = d_proj[..., 2 * R + k * N:2 * R + (k + 1) * N]
-        if g is None:
-            dst.zero_()
-        else:
-            dst.copy_(g)
+    zeros_n = lambda: torch.zeros(proj.shape[:-1] + (N,), dtype=dt, device=proj.device)
+    d_BT, d_BL, d_C = (zeros_n() if g is None else g for g in (d_BT, d_BL, d_C))
     if _fusable(x, proj.shape[-1], R):
-        d_wT, d_bT, d_wL, d_bL = _run(dtproj_bwd_op, d_dT, d_dL, deltaT, deltaL, proj, dt_projT_w, dt_projL_w, d_proj, N)
+        d_proj, d_wT, d_bT, d_wL, d_bL = _run(dtproj_bwd_op, d_dT, d_dL, deltaT, deltaL, proj, dt_projT_w, dt_projL_w,
+                                              d_BT, d_BL, d_C)
         d_wx = _run(xproj_wgrad_op, d_proj, x, N, R)
     else:
         # softplus'(z) = 1 - exp(-softplus(z)); values past the threshold of 20 give exactly 1
         sT = d_dT * (-torch.expm1(-deltaT.float())).to(dt)
         sL = d_dL * (-torch.expm1(-deltaL.float())).to(dt)
         rT, rL = proj[..., :R], proj[..., R:2 * R]
+        d_proj = torch.cat([sT @ dt_projT_w, sL @ dt_projL_w, d_BT.to(dt), d_BL.to(dt), d_C.to(dt)], dim=-1)
         d_wT = sT.reshape(-1, E).t() @ rT.reshape(-1, R)
         d_wL = sL.reshape(-1, E).t() @ rL.reshape(-1, R)
         d_bT, d_bL = sT.reshape(-1, E).sum(0), sL.reshape(-1, E).sum(0)
-        d_proj[..., :R] = sT @ dt_projT_w
-        d_proj[..., R:2 * R] = sL @ dt_projL_w
         d_wx = d_proj.reshape(-1, d_proj.shape[-1]).t() @ x.reshape(-1, E)
     d_x = d_proj @ x_proj_w
     d_AT_log = None if d_AT is None else (d_AT.float() * AT32).to(AT_log.dtype)      # d(-exp(a))/da = -exp(a) = A
@@ -385,6 +385,12 @@ class _proj_params_fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
         out, saved = _proj_forward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
+        if torch.compiler.is_compiling():
+            # Outputs that share storage with a saved intermediate (BT/BL/C are views of the projection
+            # output; a same-dtype .to() returns its argument) lose their gradient when the graph
+            # compiler traces this Function (observed with PyTorch 2.11: zero gradients, no error).
+            # Fresh copies cost three extra passes there; eager mode keeps the views.
+            out = tuple(t.clone() for t in out)
         ctx.save_for_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, out[0], out[1], *saved)
         return out
 

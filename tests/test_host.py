@@ -102,3 +102,25 @@ def test_hand_written_projection_backward_equals_autograd(dt, tol):
     for name, a, b in zip(("x",) + names, want, got):
         assert a.dtype == b.dtype and a.shape == b.shape, name
         assert (a.float() - b.float()).abs().max() <= tol * a.float().abs().max(), name
+
+
+def test_proj_params_gradients_survive_graph_capture():
+    """proj_params traced by torch.compile (no code generator: backend "eager") must give the same
+    gradients as eager mode: a custom autograd Function whose outputs alias saved tensors silently
+    lost them there."""
+    names = ("AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w", "dt_projL_b")
+    w = inputs.make_module_params(32, 16, seed=4)
+    x0 = torch.randn(2, 5, 4, 32, generator=torch.Generator().manual_seed(0))
+
+    def loss(x, *ws):
+        return sum((t * t).sum() for t in wc.proj_params(x, *ws))
+
+    def run(fn):
+        x = x0.clone().requires_grad_(True)
+        ws = [w[k].clone().requires_grad_(True) for k in names]
+        return torch.autograd.grad(fn(x, *ws), [x] + ws)
+
+    want = run(loss)
+    got = run(torch.compile(loss, backend="eager"))
+    for name, a, b in zip(("x",) + names, got, want):
+        assert float(b.abs().max()) > 0 and torch.allclose(a, b, rtol=1e-6, atol=0), name
