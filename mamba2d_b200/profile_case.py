@@ -5,7 +5,7 @@ captures and for one-off timings.
     python -m mamba2d_b200.profile_case --sweep 64,128,256,512,1024 [--reference]
     python -m mamba2d_b200.profile_case --shape 2,200,336,64 --bwd --time [--reference]
     python -m mamba2d_b200.profile_case --shape 128,56,56,64 --bwd --time --corner BR
-    python -m mamba2d_b200.profile_case --shape 128,56,56,64 --entry
+    python -m mamba2d_b200.profile_case --shape 128,56,56,64 --entry [--kernels]
 
 Inputs are seeded synthetic tensors (N = 16 states, BT/BL/C as strided views of one projection
 buffer).  ``--time`` prints CUDA-event timings; ``--reference`` also times the reference
@@ -14,7 +14,8 @@ project's own CUDA extension when it has been prebuilt (oracle/_ref/), for compa
 of getting that direction: flip copies of every per-pixel tensor, the top-left scan, flip back.
 ``--entry`` times forward + backward of the module-level entry (projections included) in both
 recomputation modes, and the same with the projections in plain PyTorch under autograd (the
-reference's formulation) around the same scan kernels.
+reference's formulation) around the same scan kernels; ``--kernels`` adds the per-kernel device
+times of one partial-recomputation step (torch.profiler, CUPTI activity records).
 """
 import argparse
 import math
@@ -91,7 +92,7 @@ def run_corner(B, H, W, E, dtype, bwd, iters):
     print(line, flush=True)
 
 
-def run_entry(B, H, W, E, dtype, iters):
+def run_entry(B, H, W, E, dtype, iters, kernels=False):
     """wavefront_scan_cuda forward + backward with module-shaped weights (A_log = log(1..N), dt_rank = E/16)."""
     from mamba2d_b200 import wavefront_cuda as wc
     N, R = 16, math.ceil(E / 16)
@@ -140,7 +141,33 @@ def run_entry(B, H, W, E, dtype, iters):
                      ("partial, projections in PyTorch", lambda: wc.wf_cuda_fn_pr.apply(x, *torch_proj(x, *w[:7]), w[7])),
                      ("full, projections in PyTorch", lambda: autograd_full.apply(x, *w))):
         line += f" {name} {timeit(lambda: step(fn), iters):.3f} ms,"
-    print(line.rstrip(","), flush=True)
+    # the same partial-recomputation step captured once in a CUDA graph and replayed
+    fn = lambda: wc.wavefront_scan_cuda(x, *w, "partial")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step(fn)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    for t in [x] + w:
+        t.grad = None
+    with torch.cuda.graph(graph):
+        fn().backward(gy)
+    line += f" partial as a CUDA graph {timeit(graph.replay, iters):.3f} ms"
+    print(line, flush=True)
+    if kernels:
+        from torch.profiler import ProfilerActivity, profile
+        fn = lambda: wc.wavefront_scan_cuda(x, *w, "partial")
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(5):
+                step(fn)
+            torch.cuda.synchronize()
+        rows = sorted((e for e in prof.key_averages() if e.device_time_total > 0), key=lambda e: -e.device_time_total)
+        total = sum(e.device_time_total for e in rows)
+        print(f"  device time per step {total / 5 / 1000:.3f} ms; kernels (average per launch, launches per step, share):")
+        for e in rows[:14]:
+            print(f"  {e.device_time_total / e.count:9.1f} us x{e.count // 5:<2d} {100 * e.device_time_total / total:5.1f} %  {e.key[:110]}")
 
 
 def run_case(B, H, W, E, dtype, bwd, iters, timed, with_ref):
@@ -178,6 +205,7 @@ def main():
     ap.add_argument("--reference", action="store_true")
     ap.add_argument("--corner", choices=("TL", "BR"), default="TL")
     ap.add_argument("--entry", action="store_true")
+    ap.add_argument("--kernels", action="store_true")
     args = ap.parse_args()
     dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
     if args.sweep:
@@ -186,7 +214,7 @@ def main():
         return
     B, H, W, E = (int(v) for v in args.shape.split(","))
     if args.entry:
-        run_entry(B, H, W, E, dtype, max(args.iters, 10))
+        run_entry(B, H, W, E, dtype, max(args.iters, 10), args.kernels)
         return
     if args.corner == "BR":
         run_corner(B, H, W, E, dtype, args.bwd, max(args.iters, 10))

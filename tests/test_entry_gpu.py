@@ -95,3 +95,47 @@ def test_entry_inside_a_compiled_graph(recomp):
     compiled = run(torch.compile(lambda x, *ws: wavefront_scan_cuda(x, *ws, recomp), backend="aot_eager"))
     for name, a, b in zip(("y", "d_x") + tuple("d_" + k for k in WNAMES), compiled, eager):
         assert rel_err(a.cpu().numpy(), b.cpu().numpy()) < 1e-5, name
+
+
+def test_entry_step_replays_from_a_cuda_graph():
+    """Forward + backward of the entry captured in a CUDA graph: every call of the library is
+    asynchronous on the capturing stream and allocates only through the caller's allocator, so the
+    step can be replayed without Python in the loop."""
+    from mamba2d_b200 import wavefront_scan_cuda
+    w = inputs.make_module_params(64, 16, seed=6)
+    gen = torch.Generator().manual_seed(12)
+    x = torch.randn(4, 14, 14, 64, generator=gen).cuda().requires_grad_(True)
+    gy = torch.randn(4, 14, 14, 64, generator=gen).cuda()
+    ws = [w[k].clone().cuda().requires_grad_(True) for k in WNAMES]
+
+    def step():
+        for t in [x] + ws:
+            t.grad = None
+        y = wavefront_scan_cuda(x, *ws)
+        y.backward(gy)
+        return y
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    y_ref = step().detach().clone()
+    g_ref = [t.grad.clone() for t in [x] + ws]
+    graph = torch.cuda.CUDAGraph()
+    for t in [x] + ws:
+        t.grad = None
+    with torch.cuda.graph(graph):
+        y = wavefront_scan_cuda(x, *ws)
+        y.backward(gy)
+    with torch.no_grad():
+        x.mul_(0.5)                        # new input values in the captured buffers
+    graph.replay()
+    with torch.no_grad():
+        x.mul_(2.0)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert rel_err(y.detach().cpu().numpy(), y_ref.cpu().numpy()) < 1e-6
+    for name, t, r in zip(("x",) + WNAMES, [x] + ws, g_ref):
+        assert rel_err(t.grad.cpu().numpy(), r.cpu().numpy()) < 1e-5, name
