@@ -89,3 +89,45 @@ def install_droppath_shim():
     sys.modules.setdefault("timm", timm)
     sys.modules.setdefault("timm.layers", layers)
     return True
+
+
+def native_scan_corner(block_cls):
+    """Optional: make the reference's ``M2DBlock`` scan from its start corner in place.
+
+    The reference block obtains ``scan_start == "BR"`` by flipping the activation on the way in and
+    the result on the way out (models/mamba2d.py:162-175); everything between those two flips other
+    than the scan acts per pixel, and the local path is taken before the first flip and added after
+    the second.  This replaces ``forward`` and ``ssm`` of the given class with versions that never
+    flip and pass ``scan_start`` to the scan instead, which is the same function of the input with
+    two full-activation copies less per odd block (and their two copies in backward).  The
+    ``double_scans`` branch keeps the reference's arithmetic: its second scan runs on the flipped
+    input and its result is averaged in as it comes, without being flipped back
+    (models/mamba2d.py:190-200).
+
+    Returns the class.  Call it after ``install()`` and after importing the model module:
+
+        from models.mamba2d import M2DBlock
+        inject.native_scan_corner(M2DBlock)
+    """
+    scan = wavefront_cuda.wavefront_scan_cuda
+
+    def ssm(self, x):
+        corner = getattr(self, "scan_start", "TL")
+        y = scan(x, self.AT_log, self.AL_log, self.x_proj.weight, self.dt_projT.weight, self.dt_projT.bias,
+                 self.dt_projL.weight, self.dt_projL.bias, self.D, self.recomp, scan_start=corner)
+        if self.double_scans:
+            other = "TL" if corner == "BR" else "BR"
+            y_b = scan(x, self.AT_log_b, self.AL_log_b, self.x_proj_b.weight, self.dt_projT_b.weight,
+                       self.dt_projT_b.bias, self.dt_projL_b.weight, self.dt_projL_b.bias, self.D_b, self.recomp,
+                       scan_start=other)
+            y = (y + y_b.flip(1, 2)) / 2
+        return y
+
+    def forward(self, x):
+        local = self.local_path(self.local_norm(x)) if self.local_path else None
+        x = self.out_proj(self.act2(self.ssm(self.act1(self.in_proj(x)))))
+        return x if local is None else x + local
+
+    block_cls.ssm = ssm
+    block_cls.forward = forward
+    return block_cls
