@@ -197,9 +197,19 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     if (d->dtype == M2D_F32) {
         a.accBT = static_cast<float*>(d->d_BT); a.accBL = static_cast<float*>(d->d_BL); a.accC = static_cast<float*>(d->d_C);
         a.accAT = static_cast<float*>(d->d_AT); a.accAL = static_cast<float*>(d->d_AL); a.accD = static_cast<float*>(d->d_D);
-        bool ok = cudaMemsetAsync(a.accBT, 0, npn * 4, st) == cudaSuccess && cudaMemsetAsync(a.accBL, 0, npn * 4, st) == cudaSuccess &&
-                  cudaMemsetAsync(a.accC, 0, npn * 4, st) == cudaSuccess && cudaMemsetAsync(a.accAT, 0, en * 4, st) == cudaSuccess &&
-                  cudaMemsetAsync(a.accAL, 0, en * 4, st) == cudaSuccess && cudaMemsetAsync(a.accD, 0, (size_t)d->E * 4, st) == cudaSuccess;
+        // the six accumulated outputs start from zero; a caller that carved them out of one buffer, in
+        // this order, gets a single memset instead of six (they are 6 x 3 us against a 230 us kernel
+        // at the smallest stage)
+        const bool adjacent = a.accBL == a.accBT + npn && a.accC == a.accBL + npn && a.accAT == a.accC + npn &&
+                              a.accAL == a.accAT + en && a.accD == a.accAL + en;
+        bool ok;
+        if (adjacent) {
+            ok = cudaMemsetAsync(a.accBT, 0, (3 * npn + 2 * en + (size_t)d->E) * 4, st) == cudaSuccess;
+        } else {
+            ok = cudaMemsetAsync(a.accBT, 0, npn * 4, st) == cudaSuccess && cudaMemsetAsync(a.accBL, 0, npn * 4, st) == cudaSuccess &&
+                 cudaMemsetAsync(a.accC, 0, npn * 4, st) == cudaSuccess && cudaMemsetAsync(a.accAT, 0, en * 4, st) == cudaSuccess &&
+                 cudaMemsetAsync(a.accAL, 0, en * 4, st) == cudaSuccess && cudaMemsetAsync(a.accD, 0, (size_t)d->E * 4, st) == cudaSuccess;
+        }
         if (!ok) return M2D_ERR_LAUNCH;
     } else {
         float* acc = reinterpret_cast<float*>(ws + L.acc);

@@ -132,9 +132,13 @@ def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
     return y
 
 
-def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False):
+def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False, shared_storage=True):
     """Fused backward with recomputation.  Returns the nine gradients
-    (d_x, d_deltaT, d_deltaL, d_AT, d_AL, d_BT, d_BL, d_C, d_D), all in ``x.dtype``."""
+    (d_x, d_deltaT, d_deltaL, d_AT, d_AL, d_BT, d_BL, d_C, d_D), all in ``x.dtype``.
+
+    With ``shared_storage`` the six reduced gradients (d_AT ... d_D) are disjoint views of one
+    allocation, which lets the library zero them with one memset; the registered operator asks
+    for separate tensors, because operator outputs must not share storage."""
     B, H, W, E, N = _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output)
     L = _lib.lib()
     dev, dt = x.device, x.dtype
@@ -143,11 +147,20 @@ def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False
         gy = grad_output.contiguous()
         keep.append(gy)
         d.gy = gy.data_ptr()
+        # the six reduced gradients are carved out of one buffer in the order the library zeroes them
+        # (d_BT, d_BL, d_C, d_AT, d_AL, d_D): one memset instead of six
+        npn, en = B * H * W * N, E * N
+        flat = torch.empty(3 * npn + 2 * en + E, dtype=dt, device=dev) if shared_storage else None
+        if flat is not None:
+            d_BT, d_BL, d_C = (flat[k * npn:(k + 1) * npn].view(B, H, W, N) for k in range(3))
+            d_AT, d_AL = (flat[3 * npn + k * en:3 * npn + (k + 1) * en].view(E, N) for k in range(2))
+            d_D = flat[3 * npn + 2 * en:]
+        else:
+            d_BT, d_BL, d_C = (torch.empty((B, H, W, N), dtype=dt, device=dev) for _ in range(3))
+            d_AT, d_AL = (torch.empty((E, N), dtype=dt, device=dev) for _ in range(2))
+            d_D = torch.empty((E,), dtype=dt, device=dev)
         outs = (torch.empty((B, H, W, E), dtype=dt, device=dev), torch.empty((B, H, W, E), dtype=dt, device=dev),
-                torch.empty((B, H, W, E), dtype=dt, device=dev), torch.empty((E, N), dtype=dt, device=dev),
-                torch.empty((E, N), dtype=dt, device=dev), torch.empty((B, H, W, N), dtype=dt, device=dev),
-                torch.empty((B, H, W, N), dtype=dt, device=dev), torch.empty((B, H, W, N), dtype=dt, device=dev),
-                torch.empty((E,), dtype=dt, device=dev))
+                torch.empty((B, H, W, E), dtype=dt, device=dev), d_AT, d_AL, d_BT, d_BL, d_C, d_D)
         for name, t in zip(("d_x", "d_dT", "d_dL", "d_AT", "d_AL", "d_BT", "d_BL", "d_C", "d_D"), outs):
             setattr(d, name, t.data_ptr())
         _workspace(d, L.m2d_scan_bwd_workspace(ctypes.byref(d)), dev, keep)
@@ -191,7 +204,7 @@ def _scan_fwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
 def scan_bwd_op(x: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, AT: torch.Tensor, AL: torch.Tensor,
                 BT: torch.Tensor, BL: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
                 grad_output: torch.Tensor, reverse: bool = False) -> list[torch.Tensor]:
-    return list(scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse))
+    return list(scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse, shared_storage=False))
 
 
 @scan_bwd_op.register_fake
