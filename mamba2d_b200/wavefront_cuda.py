@@ -242,12 +242,16 @@ def _proj_call(fn_name, d, device, keep):
     _lib.check(rc, fn_name)
 
 
-def _fusable(x, proj_cols, R):
+def _fusable(x, proj_cols, R, *others):
     """The fused projection kernels cover CUDA tensors in fp32 / bf16 with E <= 640, a dt rank of at
     most 64 and (rounded up to a power of two) at most a quarter of the channels, and channel
     counts / row pitches that are multiples of 4 (every shipped model)."""
     E = x.shape[-1]
     rank_bucket = next((b for b in (4, 8, 16, 32, 64) if R <= b), None)
+    # one dtype and one device for everything the kernels touch (under autocast the projection
+    # output can be bf16 next to fp32 weights: that case takes the PyTorch formulation)
+    if any(t.dtype != x.dtype or t.device != x.device for t in others):
+        return False
     return (x.is_cuda and x.dtype in _DTYPES and E <= _lib.PROJ_MAX_E and rank_bucket is not None
             and 4 * rank_bucket <= (E + 31) // 32 * 32 and E % 4 == 0 and proj_cols % 4 == 0)
 
@@ -348,7 +352,7 @@ def _proj_forward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_
     AL32 = -torch.exp(AL_log.float())
     proj = F.linear(x, x_proj_w)
     rT, rL, BT, BL, C = torch.split(proj, [dt_rank, dt_rank, d_state, d_state, d_state], dim=-1)
-    if _fusable(x, proj.shape[-1], dt_rank):
+    if _fusable(x, proj.shape[-1], dt_rank, proj, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
         deltaT, deltaL = _run(dtproj_fwd_op, proj, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, d_state)
     else:
         deltaT = F.softplus(F.linear(rT, dt_projT_w, dt_projT_b))
@@ -372,7 +376,7 @@ def _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, 
     d_dL = zeros_like_delta() if d_dL is None else d_dL.to(dt)
     zeros_n = lambda: torch.zeros(proj.shape[:-1] + (N,), dtype=dt, device=proj.device)
     d_BT, d_BL, d_C = (zeros_n() if g is None else g for g in (d_BT, d_BL, d_C))
-    if _fusable(x, proj.shape[-1], R):
+    if _fusable(x, proj.shape[-1], R, proj, dt_projT_w, dt_projL_w, deltaT, deltaL, d_dT, d_dL, d_BT, d_BL, d_C):
         d_proj, d_wT, d_bT, d_wL, d_bL = _run(dtproj_bwd_op, d_dT, d_dL, deltaT, deltaL, proj, dt_projT_w, dt_projL_w,
                                               d_BT, d_BL, d_C)
         d_wx = _run(xproj_wgrad_op, d_proj, x, N, R)
@@ -380,13 +384,13 @@ def _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, 
         # softplus'(z) = 1 - exp(-softplus(z)); values past the threshold of 20 give exactly 1
         sT = d_dT * (-torch.expm1(-deltaT.float())).to(dt)
         sL = d_dL * (-torch.expm1(-deltaL.float())).to(dt)
-        rT, rL = proj[..., :R], proj[..., R:2 * R]
-        d_proj = torch.cat([sT @ dt_projT_w, sL @ dt_projL_w, d_BT.to(dt), d_BL.to(dt), d_C.to(dt)], dim=-1)
+        rT, rL = proj[..., :R].to(dt), proj[..., R:2 * R].to(dt)       # (bf16 under autocast next to fp32 tensors)
+        d_proj = torch.cat([sT @ dt_projT_w.to(dt), sL @ dt_projL_w.to(dt), d_BT.to(dt), d_BL.to(dt), d_C.to(dt)], dim=-1)
         d_wT = sT.reshape(-1, E).t() @ rT.reshape(-1, R)
         d_wL = sL.reshape(-1, E).t() @ rL.reshape(-1, R)
         d_bT, d_bL = sT.reshape(-1, E).sum(0), sL.reshape(-1, E).sum(0)
         d_wx = d_proj.reshape(-1, d_proj.shape[-1]).t() @ x.reshape(-1, E)
-    d_x = d_proj @ x_proj_w
+    d_x = d_proj @ x_proj_w.to(d_proj.dtype)
     d_AT_log = None if d_AT is None else (d_AT.float() * AT32).to(AT_log.dtype)      # d(-exp(a))/da = -exp(a) = A
     d_AL_log = None if d_AL is None else (d_AL.float() * AL32).to(AL_log.dtype)
     return d_x, d_AT_log, d_AL_log, d_wx, d_wT, d_bT, d_wL, d_bL

@@ -93,3 +93,30 @@ def test_projection_ops_pass_opcheck():
     torch.library.opcheck(wc.dtproj_fwd_op, (proj, w["dt_projT_w"], w["dt_projT_b"], w["dt_projL_w"], w["dt_projL_b"], N))
     x = torch.randn(2, 5, 5, E, device="cuda")
     torch.library.opcheck(wc.xproj_wgrad_op, (proj, x, N, R))
+
+
+def test_proj_params_under_autocast_takes_the_pytorch_branch():
+    """Under autocast the x projection returns bf16 next to fp32 weights; the fused kernels want one
+    dtype, so that case runs the PyTorch formulation (forward and hand-written backward) and must
+    still agree with autograd of the reference's formulation under the same autocast."""
+    from mamba2d_b200 import proj_params
+    E = 64
+    w = _weights(E, None, seed=8)
+    g = torch.Generator().manual_seed(3)
+    x0 = torch.randn(2, 6, 6, E, generator=g)
+
+    def run(fn):
+        leaves = [x0.cuda().requires_grad_(True)] + [w[k].cuda().requires_grad_(True) for k in NAMES]
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = fn(*leaves)
+        gg = torch.Generator().manual_seed(4)
+        gs = [torch.randn(o.shape, generator=gg).to(o.device, o.dtype) for o in out]
+        grads = torch.autograd.grad(list(out), leaves, gs)
+        return [o.detach().double().cpu() for o in out], [t.double().cpu() for t in grads]
+
+    want_out, want_g = run(torch_ref.proj_params_ref)
+    got_out, got_g = run(proj_params)
+    for name, a, b in zip(OUTS, got_out, want_out):
+        assert a.shape == b.shape and rel_err(a.numpy(), b.numpy()) < 2e-2, name
+    for name, a, b in zip(("x",) + NAMES, got_g, want_g):
+        assert rel_err(a.numpy(), b.numpy()) < 4e-2, "d_" + name
