@@ -23,6 +23,8 @@ CASES = [
     ((3, 5, 4), 40, None),       # R = 3: K = 54 is not a multiple of 4, PyTorch branch
     ((1, 9, 3), 96, 5),          # K = 2R+3N = 58 is not a multiple of 4: PyTorch branch of the backward
     ((2, 33, 31), 64, 4),        # pixel count that is not a multiple of the tile
+    ((1, 1, 3), 64, 4),          # fewer pixels than one tile
+    ((1, 2, 2), 512, None),      # fewer pixels than one tile, widest block
 ]
 
 
