@@ -6,6 +6,7 @@ captures and for one-off timings.
     python -m mamba2d_b200.profile_case --shape 2,200,336,64 --bwd --time [--reference]
     python -m mamba2d_b200.profile_case --shape 128,56,56,64 --bwd --time --corner BR
     python -m mamba2d_b200.profile_case --shape 128,56,56,64 --entry [--kernels]
+    python -m mamba2d_b200.profile_case --shape 128,56,56,64 --entry --once      (one step, for ncu)
 
 Inputs are seeded synthetic tensors (N = 16 states, BT/BL/C as strided views of one projection
 buffer).  ``--time`` prints CUDA-event timings; ``--reference`` also times the reference
@@ -92,7 +93,7 @@ def run_corner(B, H, W, E, dtype, bwd, iters):
     print(line, flush=True)
 
 
-def run_entry(B, H, W, E, dtype, iters, kernels=False):
+def run_entry(B, H, W, E, dtype, iters, kernels=False, once=False):
     """wavefront_scan_cuda forward + backward with module-shaped weights (A_log = log(1..N), dt_rank = E/16)."""
     from mamba2d_b200 import wavefront_cuda as wc
     N, R = 16, math.ceil(E / 16)
@@ -135,6 +136,11 @@ def run_entry(B, H, W, E, dtype, iters, kernels=False):
             t.grad = None
         fn().backward(gy)
 
+    if once:     # one partial-recomputation step and nothing else: the command line for ncu captures
+        step(lambda: wc.wavefront_scan_cuda(x, *w, "partial"))
+        torch.cuda.synchronize()
+        print("ok")
+        return
     line = f"B={B} {H}x{W} E={E} {str(dtype).split('.')[-1]} entry fwd+bwd:"
     for name, fn in (("partial", lambda: wc.wavefront_scan_cuda(x, *w, "partial")),
                      ("full", lambda: wc.wavefront_scan_cuda(x, *w, "full")),
@@ -206,6 +212,7 @@ def main():
     ap.add_argument("--corner", choices=("TL", "BR"), default="TL")
     ap.add_argument("--entry", action="store_true")
     ap.add_argument("--kernels", action="store_true")
+    ap.add_argument("--once", action="store_true")
     args = ap.parse_args()
     dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
     if args.sweep:
@@ -214,7 +221,7 @@ def main():
         return
     B, H, W, E = (int(v) for v in args.shape.split(","))
     if args.entry:
-        run_entry(B, H, W, E, dtype, max(args.iters, 10), args.kernels)
+        run_entry(B, H, W, E, dtype, max(args.iters, 10), args.kernels, args.once)
         return
     if args.corner == "BR":
         run_corner(B, H, W, E, dtype, args.bwd, max(args.iters, 10))
