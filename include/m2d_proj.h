@@ -33,7 +33,7 @@ extern "C" {
 typedef struct m2d_proj_desc {
     uint32_t struct_bytes;     /* = sizeof(m2d_proj_desc) */
     int32_t dtype;             /* m2d_dtype of every tensor below */
-    int64_t P;                 /* pixels = B*H*W */
+    int64_t P;                 /* pixels = B*H*W; P * max(E, proj_pitch) must stay below 2^31 - 2^26 (M2D_ERR_TOO_LARGE) */
     int32_t E, R, N;           /* channels, dt rank, state size; K = 2R+3N columns are in use */
     int32_t reserved0;
     int64_t proj_pitch;        /* row pitch, in elements, of proj and d_proj (>= K) */

@@ -20,14 +20,14 @@ constexpr int kProjIters = 8;          // pixels per thread per tile
 
 struct ProjPlan {
     int EB, PS, threads, TP, RB, gx;
-    long long ntiles;
+    int ntiles;
     // x-projection weight gradient
     int tilesK, tilesE, slabs, rows_per_slab, K;
     size_t dt_partials, wg_partials;   // bytes
 };
 
 struct ProjArgs {
-    long long P, pitch, ntiles;
+    int P, pitch, ntiles;              // every element index fits 31 bits (checked on the host)
     int E, R, EB, PS, TP;
     const void *proj, *WT, *WL, *bT, *bL;
     void *dT, *dL;
@@ -37,7 +37,7 @@ struct ProjArgs {
 };
 
 struct WgArgs {
-    long long P, pitch;
+    int P, pitch;
     int E, K, rows_per_slab;
     const void *x, *d_proj;
     float* partials;                   // [slab][K][E]
@@ -57,7 +57,8 @@ static int check_proj(const m2d_proj_desc* d) {
         if (4 * RB > EB) return M2D_ERR_SHAPE;
     }
     const long long widest = d->proj_pitch > d->E ? d->proj_pitch : d->E;
-    if (d->P * widest >= (1ll << 40)) return M2D_ERR_TOO_LARGE;
+    // the kernels use 31-bit element indices, as the scan does (with room for the look-ahead of one grid of tiles)
+    if (d->P * widest >= (1ll << 31) - (1ll << 26)) return M2D_ERR_TOO_LARGE;
     return M2D_OK;
 }
 
@@ -69,8 +70,8 @@ static ProjPlan plan_proj(const m2d_proj_desc* d) {
     p.threads = p.EB * p.PS;
     p.TP = kProjIters * p.PS;
     p.RB = d->R <= 4 ? 4 : d->R <= 8 ? 8 : d->R <= 16 ? 16 : d->R <= 32 ? 32 : 64;
-    p.ntiles = (d->P + p.TP - 1) / p.TP;
-    p.gx = (int)(p.ntiles < 2ll * sms ? p.ntiles : 2ll * sms);
+    p.ntiles = (int)((d->P + p.TP - 1) / p.TP);
+    p.gx = p.ntiles < 2 * sms ? p.ntiles : 2 * sms;
     p.dt_partials = (size_t)2 * p.gx * (p.RB + 1) * p.EB * sizeof(float);
     p.K = 2 * d->R + 3 * d->N;
     p.tilesK = (p.K + 63) / 64;
@@ -87,7 +88,31 @@ static ProjPlan plan_proj(const m2d_proj_desc* d) {
 }
 
 // softplus with the reference's threshold of 20 (torch.nn.functional.softplus defaults)
-__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(__expf(z)); }
+// log1p(t) for t in (0, 1] as 2*atanh(t / (2 + t)): the argument stays below 1/3, where seven terms of
+// the series are exact to fp32 rounding (next term 2 s^15 / 15 < 1e-8 of the result); half the
+// instructions of log1pf, which was a third of the forward kernel.
+__device__ __forceinline__ float log1p_unit(float t) {
+    const float s = __fdividef(t, 2.f + t), s2 = s * s;
+    float p = 1.f / 13.f;
+    p = fmaf(p, s2, 1.f / 11.f);
+    p = fmaf(p, s2, 1.f / 9.f);
+    p = fmaf(p, s2, 1.f / 7.f);
+    p = fmaf(p, s2, 1.f / 5.f);
+    p = fmaf(p, s2, 1.f / 3.f);
+    p = fmaf(p, s2, 1.f);
+    return 2.f * s * p;
+}
+// softplus(z) = max(z, 0) + log1p(exp(-|z|)); past the reference's threshold of 20 the second term is
+// below half an ulp of z, so the threshold of torch.nn.functional.softplus needs no branch
+__device__ __forceinline__ float softplus_f(float z) {
+    // exp(-|z|) = 2^(a + e): a is the rounded product with log2(e); e collects what that rounding and
+    // the rounding of the constant lost (without it the error grows with |z|: 3e-6 at |z| = 60)
+    const float m = -fabsf(z);
+    const float a = m * kLog2e;
+    const float e = fmaf(m, kLog2e, -a) + m * 1.92596299e-8f;
+    const float t = ex2(a) * fmaf(e, kLn2, 1.f);
+    return fmaxf(z, 0.f) + log1p_unit(t);
+}
 
 // ------------------------------------------------------------------------------------------------
 // delta = softplus(r @ W^T + b).  grid (ctas, 2 directions); block = EB channels x PS pixels.
@@ -106,25 +131,25 @@ __global__ void __launch_bounds__(MAXT) dtproj_fwd_kernel(const ProjArgs a) {
 
     float w[RB];
 #pragma unroll
-    for (int r = 0; r < RB; ++r) w[r] = (e_ok && r < a.R) ? load1(W, (long long)te * a.R + r) : 0.f;
+    for (int r = 0; r < RB; ++r) w[r] = (e_ok && r < a.R) ? load1(W, te * a.R + r) : 0.f;
     const float b = e_ok ? load1(bias, te) : 0.f;
 
     // The rank-R rows of the next tile are fetched into registers while this tile is computed
     // (TP*RB <= 2*blockDim is guaranteed by the host: two values per thread at most).
     const int tile_elems = a.TP * RB;
-    auto fetch_rows = [&](long long tile, float (&v)[2]) {
+    auto fetch_rows = [&](int tile, float (&v)[2]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int idx = threadIdx.x + h * blockDim.x;
             const int pp = idx / RB, r = idx % RB;
-            const long long p = tile * a.TP + pp;
+            const int p = tile * a.TP + pp;
             v[h] = (idx < tile_elems && r < a.R && p < a.P && tile < a.ntiles) ? load1(proj, p * a.pitch + col0 + r) : 0.f;
         }
     };
     float nxt[2];
     fetch_rows(blockIdx.x, nxt);
-    for (long long tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x) {
-        const long long p0 = tile * a.TP;
+    for (int tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x) {
+        const int p0 = tile * a.TP;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int idx = threadIdx.x + h * blockDim.x;
@@ -133,7 +158,7 @@ __global__ void __launch_bounds__(MAXT) dtproj_fwd_kernel(const ProjArgs a) {
         __syncthreads();
         fetch_rows(tile + gridDim.x, nxt);
         io_t* dst = out + (p0 + ps) * a.E + te;
-        const long long row_step = (long long)a.PS * a.E;
+        const int row_step = a.PS * a.E;
 #pragma unroll
         for (int k = 0; k < kProjIters; ++k) {
             const int pp = k * a.PS + ps;
@@ -199,7 +224,7 @@ __global__ void __launch_bounds__(MAXT) dtproj_bwd_kernel(const ProjArgs a) {
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
             const int r = h * RL + rl, ch = e_slice + e;
-            wreg[h][e] = (ch < a.E && r < a.R) ? load1(W, (long long)ch * a.R + r) : 0.f;
+            wreg[h][e] = (ch < a.E && r < a.R) ? load1(W, ch * a.R + r) : 0.f;
         }
 
     float acc[RB];
@@ -208,22 +233,22 @@ __global__ void __launch_bounds__(MAXT) dtproj_bwd_kernel(const ProjArgs a) {
     float accb = 0.f;
 
     const int tile_elems = a.TP * RB;
-    auto fetch_rows = [&](long long tile, float (&v)[2]) {
+    auto fetch_rows = [&](int tile, float (&v)[2]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int idx = threadIdx.x + h * blockDim.x;
             const int pp = idx / RB, r = idx % RB;
-            const long long p = tile * a.TP + pp;
+            const int p = tile * a.TP + pp;
             v[h] = (idx < tile_elems && r < a.R && p < a.P && tile < a.ntiles) ? load1(proj, p * a.pitch + col0 + r) : 0.f;
         }
     };
     // The tile's g and delta rows (TP consecutive pixels = one contiguous chunk of each tensor) are
     // copied to shared memory with cp.async, one tile ahead, in pieces of 4 elements.
     const int tile_chunk = a.TP * a.E;                       // elements per tensor per tile
-    auto issue_inputs = [&](long long tile, int buf) {
+    auto issue_inputs = [&](int tile, int buf) {
         io_t* dst_g = tiles + (size_t)(buf * 2) * tile_chunk;
         io_t* dst_d = dst_g + tile_chunk;
-        const long long base = tile * a.TP * a.E;
+        const int base = tile * a.TP * a.E;
         for (int piece = threadIdx.x; piece * 4 < tile_chunk; piece += blockDim.x) {
             const int off = piece * 4;
             const bool ok = tile < a.ntiles && tile * a.TP + off / a.E < a.P;
@@ -248,8 +273,8 @@ __global__ void __launch_bounds__(MAXT) dtproj_bwd_kernel(const ProjArgs a) {
     fetch_rows(blockIdx.x, nxt);
     issue_inputs(blockIdx.x, 0);
     int buf = 0;
-    for (long long tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x, buf ^= 1) {
-        const long long p0 = tile * a.TP;
+    for (int tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x, buf ^= 1) {
+        const int p0 = tile * a.TP;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int idx = threadIdx.x + h * blockDim.x;
@@ -385,8 +410,8 @@ __global__ void __launch_bounds__(256) xproj_wgrad_kernel(const WgArgs a) {
     const io_t* B = static_cast<const io_t*>(a.x);
     const int tid = threadIdx.x, te = tid & 15, tk = tid >> 4;
     const int e0 = blockIdx.y * 64, k0 = blockIdx.z * 64;
-    const long long row0 = (long long)blockIdx.x * a.rows_per_slab;
-    long long row_end = row0 + a.rows_per_slab;
+    const int row0 = blockIdx.x * a.rows_per_slab;
+    int row_end = row0 + a.rows_per_slab;
     if (row_end > a.P) row_end = a.P;
     const int chunks = (int)((row_end - row0 + 31) / 32);
 
@@ -395,7 +420,7 @@ __global__ void __launch_bounds__(256) xproj_wgrad_kernel(const WgArgs a) {
     auto fetch = [&](int chunk, float4 (&ra)[2], float4 (&rb)[2]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const long long p = row0 + (long long)chunk * 32 + lr + 16 * h;
+            const int p = row0 + chunk * 32 + lr + 16 * h;
             const bool row_ok = p < row_end;
             const int ka = k0 + lc * 4, eb = e0 + lc * 4;
             ra[h] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -476,7 +501,7 @@ __global__ void xproj_wgrad_finalize(const float* __restrict__ partials, int sla
 // ------------------------------------------------------------------------------------------------
 static ProjArgs proj_args(const m2d_proj_desc* d, const ProjPlan& p) {
     ProjArgs a;
-    a.P = d->P; a.pitch = d->proj_pitch; a.ntiles = p.ntiles;
+    a.P = (int)d->P; a.pitch = (int)d->proj_pitch; a.ntiles = p.ntiles;
     a.E = d->E; a.R = d->R; a.EB = p.EB; a.PS = p.PS; a.TP = p.TP;
     a.proj = d->proj; a.WT = d->WT; a.WL = d->WL; a.bT = d->bT; a.bL = d->bL;
     a.dT = d->dT; a.dL = d->dL; a.g_dT = d->g_dT; a.g_dL = d->g_dL;
@@ -534,7 +559,7 @@ template <typename io_t>
 static int launch_wgrad(const m2d_proj_desc* d, cudaStream_t st) {
     const ProjPlan p = plan_proj(d);
     WgArgs a;
-    a.P = d->P; a.pitch = d->proj_pitch; a.E = d->E; a.K = p.K; a.rows_per_slab = p.rows_per_slab;
+    a.P = (int)d->P; a.pitch = (int)d->proj_pitch; a.E = d->E; a.K = p.K; a.rows_per_slab = p.rows_per_slab;
     a.x = d->x; a.d_proj = d->d_proj;
     a.partials = static_cast<float*>(d->workspace);
     xproj_wgrad_kernel<io_t><<<dim3(p.slabs, p.tilesE, p.tilesK), 256, 0, st>>>(a);

@@ -252,6 +252,8 @@ def _fusable(x, proj_cols, R, *others):
     # output can be bf16 next to fp32 weights: that case takes the PyTorch formulation)
     if any(t.dtype != x.dtype or t.device != x.device for t in others):
         return False
+    if (x.numel() // E) * max(E, proj_cols) >= (1 << 31) - (1 << 26):      # 31-bit element indices in the kernels
+        return False
     return (x.is_cuda and x.dtype in _DTYPES and E <= _lib.PROJ_MAX_E and rank_bucket is not None
             and 4 * rank_bucket <= (E + 31) // 32 * 32 and E % 4 == 0 and proj_cols % 4 == 0)
 
