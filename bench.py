@@ -342,8 +342,30 @@ def m2dt_scan_layers(dev, batch=128, iters=5):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
-    return {"images_per_s": batch / (ms * 1e-3), "ms": ms, "batch": batch, "dtype": "bf16",
-            "what": "6 scan layers of M2D-T (3x D=64@56x56, 3x D=128@28x28) through wavefront_scan_cuda incl. projections"}
+
+    # the same six layers in training: forward + backward with gradients for x and every weight
+    train = []
+    for x, ws in layers:
+        train.append((x.clone().requires_grad_(True), [t.clone().requires_grad_(True) for t in ws], torch.randn_like(x)))
+
+    def run_train():
+        for x, ws, gy in train:
+            for t in [x] + ws:
+                t.grad = None
+            wavefront_scan_cuda(x, *ws).backward(gy)
+    for _ in range(2):
+        run_train()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        run_train()
+    e1.record()
+    torch.cuda.synchronize()
+    train_ms = e0.elapsed_time(e1) / iters
+    return {"images_per_s": batch / (ms * 1e-3), "ms": ms, "train_ms": train_ms, "train_images_per_s": batch / (train_ms * 1e-3),
+            "batch": batch, "dtype": "bf16",
+            "what": "6 scan layers of M2D-T (3x D=64@56x56, 3x D=128@28x28) through wavefront_scan_cuda incl. projections; "
+                    "ms = forward under inference mode, train_ms = forward + backward"}
 
 
 def reference_gpu(devin, dtype, iters=2):
