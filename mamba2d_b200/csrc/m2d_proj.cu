@@ -29,6 +29,7 @@ struct ProjPlan {
 struct ProjArgs {
     int P, pitch, ntiles;              // every element index fits 31 bits (checked on the host)
     int E, R, EB, PS, TP;
+    int wide16;                        // bf16 backward: rows and pointers allow 16-byte copies
     const void *proj, *WT, *WL, *bT, *bL;
     void *dT, *dL;
     const void *g_dT, *g_dL;
@@ -249,10 +250,14 @@ __global__ void __launch_bounds__(MAXT) dtproj_bwd_kernel(const ProjArgs a) {
         io_t* dst_g = tiles + (size_t)(buf * 2) * tile_chunk;
         io_t* dst_d = dst_g + tile_chunk;
         const int base = tile * a.TP * a.E;
-        for (int piece = threadIdx.x; piece * 4 < tile_chunk; piece += blockDim.x) {
-            const int off = piece * 4;
+        // 16-byte pieces (4 fp32 or 8 bf16 elements, L2-only copies) where rows allow it and both
+        // tensors are 16-byte aligned; 8-byte pieces for bf16 rows that are only a multiple of 4
+        const bool wide = sizeof(io_t) == 4 || a.wide16;
+        const int pe = wide ? 16 / (int)sizeof(io_t) : 4;
+        for (int piece = threadIdx.x; piece * pe < tile_chunk; piece += blockDim.x) {
+            const int off = piece * pe;
             const bool ok = tile < a.ntiles && tile * a.TP + off / a.E < a.P;
-            if (sizeof(io_t) == 4) {
+            if (wide) {
                 cp_async16_if(ok, smem_u32(dst_g + off), g + base + off);
                 cp_async16_if(ok, smem_u32(dst_d + off), delta + base + off);
                 if (!ok) {
@@ -507,6 +512,7 @@ static ProjArgs proj_args(const m2d_proj_desc* d, const ProjPlan& p) {
     a.dT = d->dT; a.dL = d->dL; a.g_dT = d->g_dT; a.g_dL = d->g_dL;
     a.d_proj = d->d_proj;
     a.partials = static_cast<float*>(d->workspace);
+    a.wide16 = d->E % 8 == 0 && aligned(d->g_dT, 16) && aligned(d->g_dL, 16) && aligned(d->dT, 16) && aligned(d->dL, 16);
     return a;
 }
 
