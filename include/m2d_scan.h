@@ -10,7 +10,9 @@
  * the reference's autograd Function wf_cuda_fn_pr (models/kernels/wavefront_cuda.py:146-196):
  *   forward   (x, dT, dL, AT, AL, BT, BL, C, D)        -> y
  *   backward  (x, dT, dL, AT, AL, BT, BL, C, D, gy)    -> nine gradients
- * so that the 5-D hidden state never has to exist in memory.
+ * so that the forward pass never materialises the 5-D hidden state and autograd never saves it (the
+ * backward pass recomputes it into its own workspace, as the reference's partial-recomputation
+ * mode does: wavefront_cuda.py:172-173).
  *
  * Conventions
  *   - plain C types only; every pointer is a DEVICE pointer unless stated otherwise;
@@ -31,7 +33,7 @@
 extern "C" {
 #endif
 
-#define M2D_ABI_VERSION 2
+#define M2D_ABI_VERSION 3
 
 typedef enum m2d_dtype {
     M2D_F32 = 0,   /* float in memory, float arithmetic */
@@ -67,6 +69,16 @@ typedef enum m2d_status {
  * scan itself runs in reverse.
  */
 #define M2D_SCAN_REVERSE 1u
+
+/*
+ * M2D_SCAN_TEST_WITHHOLD: test hook, rejected with M2D_ERR_FLAGS unless the environment variable
+ * M2D_TEST_HOOKS is 1.  In a launch that runs several CTAs per image, the CTA that owns the first
+ * band of image 0 never publishes that band's column counter and every wait gives up after a few
+ * hundred tries instead of a million: the CTA below runs out of patience, the kernel returns
+ * normally and the status word is nonzero.  Nothing faults or hangs; the outputs are void.  It
+ * exists so that the give-up path of the bounded waits can be exercised by a test.
+ */
+#define M2D_SCAN_TEST_WITHHOLD 0x100u
 
 /*
  * Problem descriptor.  Tensor layouts are the ones the reference op receives:
@@ -105,9 +117,9 @@ int m2d_abi_version(void);
 const char *m2d_strerror(int status);
 
 /*
- * Bytes of scratch m2d_scan_fwd / m2d_scan_bwd need for this problem on the current device
- * (0 is possible).  Replaces the reference's Python-side allocations of hs / dDAT / dDAL / omega
- * (wavefront_cuda.py:152, :181-183).  Returns 0 for an invalid descriptor.
+ * Bytes of scratch m2d_scan_fwd / m2d_scan_bwd need for this problem on the current device (never
+ * 0: the scratch starts with a status word).  Replaces the reference's Python-side allocations of
+ * hs / dDAT / dDAL / omega (wavefront_cuda.py:152, :181-183).  Returns 0 for an invalid descriptor.
  */
 uint64_t m2d_scan_fwd_workspace(const m2d_scan_desc *desc);
 uint64_t m2d_scan_bwd_workspace(const m2d_scan_desc *desc);
@@ -120,15 +132,30 @@ uint64_t m2d_scan_bwd_workspace(const m2d_scan_desc *desc);
 int m2d_scan_fwd(const m2d_scan_desc *desc, void *stream);
 
 /*
- * Large maps with few images run several CTAs per image that wait on one another with bounded
- * polling.  If such a wait ever gives up (it cannot when the kernel has the GPU to itself), the
- * kernel still terminates and writes a nonzero int32 status word into the workspace.  This returns
- * the byte offset of that word inside the workspace for this problem, or -1 if the problem does
- * not use cross-CTA waits.  Read the word after synchronising the stream.  No counterpart in the
- * reference (its launches are serialised by the host).
+ * With few images on a large map several CTAs share an image and wait on one another through
+ * global memory (inside a CTA the row-warps meet at block barriers with uniform trip counts).  Every
+ * wait between CTAs is bounded.  If one ever gives up (it cannot when the kernel has the GPU
+ * to itself), all later waits return at once, the kernel terminates normally and leaves a nonzero
+ * int32 status word in the workspace; the outputs are then void.  These return the byte offset of
+ * that word inside the workspace (0 today), or -1 for an invalid descriptor.  Read the word after
+ * synchronising the stream.  m2d_scan_*_chain return how many CTAs share one image for this problem
+ * on the current device (1: none do; 0: invalid descriptor) -- launches with more than one are the
+ * ones whose waits cross CTAs.  No counterpart in the reference (its launches are serialised by the
+ * host).
  */
 int64_t m2d_scan_fwd_status_offset(const m2d_scan_desc *desc);
 int64_t m2d_scan_bwd_status_offset(const m2d_scan_desc *desc);   /* same, for m2d_scan_bwd's workspace */
+int m2d_scan_fwd_chain(const m2d_scan_desc *desc);
+int m2d_scan_bwd_chain(const m2d_scan_desc *desc);
+
+/*
+ * The rule every launch applies when it picks, or has to shorten, the number of CTAs per image:
+ * at most one CTA per band, and when CTAs own more than one band each (the chain closes into a
+ * ring) fewer than one row of steps divided by the rows per band, so that the head of the ring
+ * never waits on data that waits on the head.  Host-side arithmetic only; returns 0 for
+ * non-positive arguments.  No counterpart in the reference.
+ */
+int m2d_scan_chain_bound(int want, int nbands, int steps_per_row, int rows_per_band);
 
 /*
  * Backward with recomputation of the hidden state: all nine gradients of the forward.
@@ -151,15 +178,20 @@ int m2d_scan_bwd(const m2d_scan_desc *desc, void *stream);
  *
  *   - The array is M2D_NOALLOC_SCRATCH_BYTES (32 MiB) and every GPU that loads the library keeps
  *     it until the process exits.
- *   - A problem needing more scratch than that returns M2D_ERR_TOO_LARGE before any device work
- *     (the need is what m2d_scan_fwd_workspace() reports).
- *   - All calls on a device share the array.  Nothing in it must be zero on entry, but calls that
- *     overlap in time on one GPU race on it: keep them on one stream or order them with events.
+ *   - A problem needing more scratch than that returns M2D_ERR_TOO_LARGE before any device work.
+ *     m2d_scan_fwd_noalloc_need() reports the need: a status word plus one ring of W slots of 2 KiB
+ *     per CTA when the map has more rows than a CTA has row-warps (8), with at most two CTAs per SM.
+ *     This entry always runs one CTA per (image, channel group), so its need can differ from what
+ *     m2d_scan_fwd_workspace() reports for the same problem.
+ *   - All calls on a device share the array.  The call clears the one word that must start at
+ *     zero itself, but calls that overlap in time on one GPU race on the array: keep them on one
+ *     stream or order them with events.
  *   - The first call on each device resolves the array's device address and caches it; issue
  *     that first call before any stream capture on that device.
  */
 #define M2D_NOALLOC_SCRATCH_BYTES (32u << 20)
 int m2d_scan_fwd_noalloc(const m2d_scan_desc *desc, void *stream);
+uint64_t m2d_scan_fwd_noalloc_need(const m2d_scan_desc *desc);   /* bytes of the array this problem would use; 0 if invalid */
 
 #ifdef __cplusplus
 }

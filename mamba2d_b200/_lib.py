@@ -11,11 +11,13 @@ LIB_PATH = os.environ.get("M2D_SCAN_LIB", os.path.join(HERE, "libm2d_scan.so")) 
 
 M2D_F32, M2D_BF16 = 0, 1
 M2D_SCAN_REVERSE = 1
-ABI_VERSION = 2
+M2D_SCAN_TEST_WITHHOLD = 0x100
+ABI_VERSION = 3
 NOALLOC_SCRATCH_BYTES = 32 << 20     # M2D_NOALLOC_SCRATCH_BYTES in include/m2d_scan.h
 
 EXPORTS = ("m2d_abi_version", "m2d_strerror", "m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace",
-           "m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc", "m2d_scan_fwd_status_offset", "m2d_scan_bwd_status_offset",
+           "m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc", "m2d_scan_fwd_noalloc_need", "m2d_scan_fwd_status_offset",
+           "m2d_scan_bwd_status_offset", "m2d_scan_fwd_chain", "m2d_scan_bwd_chain", "m2d_scan_chain_bound",
            "m2d_proj_workspace", "m2d_dtproj_fwd", "m2d_dtproj_bwd", "m2d_xproj_wgrad")
 PROJ_MAX_E, PROJ_MAX_R = 640, 64     # M2D_PROJ_MAX_E / M2D_PROJ_MAX_R in include/m2d_proj.h
 
@@ -67,7 +69,12 @@ def lib():
         L.m2d_abi_version.restype = ctypes.c_int
         L.m2d_strerror.restype = ctypes.c_char_p
         L.m2d_strerror.argtypes = [ctypes.c_int]
-        for name in ("m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace"):
+        for name in ("m2d_scan_fwd_chain", "m2d_scan_bwd_chain"):
+            getattr(L, name).restype = ctypes.c_int
+            getattr(L, name).argtypes = [ctypes.POINTER(ScanDesc)]
+        L.m2d_scan_chain_bound.restype = ctypes.c_int
+        L.m2d_scan_chain_bound.argtypes = [ctypes.c_int] * 4
+        for name in ("m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace", "m2d_scan_fwd_noalloc_need"):
             getattr(L, name).restype = ctypes.c_uint64
             getattr(L, name).argtypes = [ctypes.POINTER(ScanDesc)]
         for name in ("m2d_scan_fwd_status_offset", "m2d_scan_bwd_status_offset"):

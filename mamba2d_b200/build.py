@@ -29,7 +29,7 @@ def _nvcc():
 def _deps():
     out = [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE) if f.endswith(".h")]
     for f in os.listdir(CSRC):
-        if f.endswith((".cu", ".cuh")) and f != "mufu_probe.cu":
+        if f.endswith((".cu", ".cuh")):
             out.append(os.path.join(CSRC, f))
     return out
 
@@ -79,16 +79,5 @@ def build(force=False, verbose=False):
     return OUT
 
 
-def build_probe():
-    """The stand-alone instruction-rate probe (csrc/mufu_probe.cu) -> mamba2d_b200/mufu_probe."""
-    out = os.path.join(HERE, "mufu_probe")
-    cmd = [_nvcc(), "-ccbin", "/usr/bin/g++", *ARCH, "-O3", os.path.join(CSRC, "mufu_probe.cu"), "-o", out]
-    subprocess.run(cmd, check=True)
-    return out
-
-
 if __name__ == "__main__":
-    if "--probe" in sys.argv:
-        print(build_probe())
-    else:
-        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv or "-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv or "-v" in sys.argv))

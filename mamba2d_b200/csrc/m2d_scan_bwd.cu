@@ -2,40 +2,40 @@
 // followed by a small kernel that casts the fp32 accumulators of the reduced gradients.
 #include <cstdlib>
 
-#include "plan.cuh"
+#include "launch.cuh"
 #include "sweep_bwd.cuh"
 
 namespace m2d {
 
 // Workspace layout of the backward pass (all regions 256-byte aligned):
-//   hs     state record written by the recompute sweep     B*groups*H*W*2 KiB
-//   ring   per-CTA band-boundary ring                      ctas*W*2 KiB   (only if nbands > 1)
-//   acc    bf16 I/O only: fp32 accumulators 3 x [B*H*W][N] | 2 x [E][N] | [E], zeroed before the
-//          main kernel and cast by a second kernel.  With fp32 I/O the kernel accumulates straight
-//          into the caller's (zeroed) gradient tensors and this region is empty.
+//   status   one word, nonzero if a wait between CTAs gave up
+//   counters chained CTAs only: two column counters per band (recompute sweep, adjoint sweep)
+//   ring     per-CTA band-boundary ring, ctas*W*2 KiB (only if nbands > 1); with chained CTAs one
+//            boundary row per band instead (h downwards in the recompute sweep, pT upwards in the
+//            adjoint sweep)
+//   hs       state record written by the recompute sweep     B*groups*H*W*2 KiB (1 KiB with bf16 I/O)
+//   acc      bf16 I/O only: fp32 accumulators 3 x [B*H*W][N] | 2 x [E][N] | [E], zeroed before the
+//            main kernel and cast by a second kernel.  With fp32 I/O the kernel accumulates straight
+//            into the caller's (zeroed) gradient tensors and this region is empty.
 struct BwdLayout {
-    size_t hs, ring, counters, counter_bytes, acc, acc_bytes, total;
+    size_t counters, ring, hs, acc, acc_bytes, total;
 };
 
 inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
     BwdLayout L;
-    size_t off = 0;
-    L.hs = off;
-    off += align256((size_t)d->B * p.groups * d->H * d->W * (d->dtype == M2D_F32 ? 128 : 64) * sizeof(float4));
+    size_t off = kStatusBytes;
+    L.counters = off;
     L.ring = off;
-    L.counters = 0;
-    L.counter_bytes = 0;
     if (p.chain > 1) {
-        // chained CTAs: one boundary row per band (h downwards in the recompute sweep, pT upwards in the
-        // adjoint sweep), two column counters per band and a status word
         const size_t nband = (size_t)d->B * p.groups * p.nbands;
+        off += align256(2 * nband * sizeof(int));
+        L.ring = off;
         off += align256(nband * d->W * kSlotF4 * sizeof(float4));
-        L.counters = off;
-        L.counter_bytes = align256((2 * nband + 1) * sizeof(int));
-        off += L.counter_bytes;
     } else if (p.nbands > 1) {
         off += align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
     }
+    L.hs = off;
+    off += align256((size_t)d->B * p.groups * d->H * d->W * (d->dtype == M2D_F32 ? 128 : 64) * sizeof(float4));
     L.acc = off;
     L.acc_bytes = 0;
     if (d->dtype != M2D_F32) {
@@ -57,15 +57,7 @@ inline Plan plan_bwd(const m2d_scan_desc* d) {
     {
         const long long slots = (long long)(12 / p.warps > 0 ? 12 / p.warps : 1) * sm_count();
         const long long ctas = (long long)p.grid_x * p.groups;
-        if (p.nbands > 1 && ctas * 2 <= slots) {
-            long long c = slots / ctas;
-            if (c > p.nbands) c = p.nbands;
-            if (c < p.nbands) {
-                const long long lim = d->W / p.Rb - 1;   // ring bound, see plan_fwd
-                if (c > lim) c = lim;
-            }
-            p.chain = c < 1 ? 1 : (int)c;
-        }
+        if (p.nbands > 1 && ctas * 2 <= slots) p.chain = bound_chain(slots / ctas, p.nbands, d->W, p.Rb);
     }
     p.scratch = bwd_layout(d, p).total;
     return p;
@@ -174,22 +166,17 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     const BwdLayout L = bwd_layout(d, pl);
     char* ws = static_cast<char*>(d->workspace);
     ScanArgs a;
-    a.B = d->B; a.H = d->H; a.W = d->W; a.E = d->E; a.N = d->N;
-    a.dir = (d->flags & M2D_SCAN_REVERSE) ? -1 : 1;
-    a.x = d->x; a.dT = d->dT; a.dL = d->dL; a.AT = d->AT; a.AL = d->AL;
-    a.BT = d->BT; a.BL = d->BL; a.C = d->C; a.D = d->D;
-    a.pBT = d->BT_pitch; a.pBL = d->BL_pitch; a.pC = d->C_pitch;
-    a.y = nullptr;
+    fill_common_args(a, d, pl);
+    a.status = reinterpret_cast<int*>(ws);
     a.ring = reinterpret_cast<float4*>(ws + L.ring);
-    a.Rb = pl.Rb; a.nbands = pl.nbands;
-    a.chain = pl.chain; a.bnd = nullptr; a.progress = nullptr; a.status = nullptr;
+    size_t zero_bytes = sizeof(int);
     if (pl.chain > 1) {
         const size_t nband = (size_t)d->B * pl.groups * pl.nbands;
         a.bnd = reinterpret_cast<float4*>(ws + L.ring);
         a.progress = reinterpret_cast<int*>(ws + L.counters);
-        a.status = a.progress + 2 * nband;
-        if (cudaMemsetAsync(a.progress, 0, (2 * nband + 1) * sizeof(int), st) != cudaSuccess) return M2D_ERR_LAUNCH;
+        zero_bytes = kStatusBytes + 2 * nband * sizeof(int);
     }
+    if (cudaMemsetAsync(ws, 0, zero_bytes, st) != cudaSuccess) return M2D_ERR_LAUNCH;
     a.gy = d->gy;
     a.hs = reinterpret_cast<float4*>(ws + L.hs);
     a.d_x = d->d_x; a.d_dT = d->d_dT; a.d_dL = d->d_dL;
@@ -197,18 +184,21 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     if (d->dtype == M2D_F32) {
         a.accBT = static_cast<float*>(d->d_BT); a.accBL = static_cast<float*>(d->d_BL); a.accC = static_cast<float*>(d->d_C);
         a.accAT = static_cast<float*>(d->d_AT); a.accAL = static_cast<float*>(d->d_AL); a.accD = static_cast<float*>(d->d_D);
-        // the six accumulated outputs start from zero; a caller that carved them out of one buffer, in
-        // this order, gets a single memset instead of six (they are 6 x 3 us against a 230 us kernel
-        // at the smallest stage)
-        const bool adjacent = a.accBL == a.accBT + npn && a.accC == a.accBL + npn && a.accAT == a.accC + npn &&
-                              a.accAL == a.accAT + en && a.accD == a.accAL + en;
+        // the six accumulated outputs start from zero; a caller that carved the three per-pixel ones
+        // out of one buffer and the three per-channel ones out of another, in this order, gets two
+        // memsets instead of six (they are 3 us each against a 200 us kernel at the smallest stage)
+        const bool big_adjacent = a.accBL == a.accBT + npn && a.accC == a.accBL + npn;
+        const bool small_adjacent = a.accAL == a.accAT + en && a.accD == a.accAL + en;
         bool ok;
-        if (adjacent) {
+        if (big_adjacent && a.accAT == a.accC + npn && small_adjacent) {
             ok = cudaMemsetAsync(a.accBT, 0, (3 * npn + 2 * en + (size_t)d->E) * 4, st) == cudaSuccess;
         } else {
-            ok = cudaMemsetAsync(a.accBT, 0, npn * 4, st) == cudaSuccess && cudaMemsetAsync(a.accBL, 0, npn * 4, st) == cudaSuccess &&
-                 cudaMemsetAsync(a.accC, 0, npn * 4, st) == cudaSuccess && cudaMemsetAsync(a.accAT, 0, en * 4, st) == cudaSuccess &&
-                 cudaMemsetAsync(a.accAL, 0, en * 4, st) == cudaSuccess && cudaMemsetAsync(a.accD, 0, (size_t)d->E * 4, st) == cudaSuccess;
+            ok = big_adjacent ? cudaMemsetAsync(a.accBT, 0, 3 * npn * 4, st) == cudaSuccess
+                              : (cudaMemsetAsync(a.accBT, 0, npn * 4, st) == cudaSuccess && cudaMemsetAsync(a.accBL, 0, npn * 4, st) == cudaSuccess &&
+                                 cudaMemsetAsync(a.accC, 0, npn * 4, st) == cudaSuccess);
+            ok = ok && (small_adjacent ? cudaMemsetAsync(a.accAT, 0, (2 * en + (size_t)d->E) * 4, st) == cudaSuccess
+                                       : (cudaMemsetAsync(a.accAT, 0, en * 4, st) == cudaSuccess && cudaMemsetAsync(a.accAL, 0, en * 4, st) == cudaSuccess &&
+                                          cudaMemsetAsync(a.accD, 0, (size_t)d->E * 4, st) == cudaSuccess));
         }
         if (!ok) return M2D_ERR_LAUNCH;
     } else {
@@ -217,34 +207,10 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
         a.accAT = acc + 3 * npn; a.accAL = a.accAT + en; a.accD = a.accAL + en;
         if (cudaMemsetAsync(acc, 0, L.acc_bytes, st) != cudaSuccess) return M2D_ERR_LAUNCH;
     }
-    dim3 block(pl.warps * 32);
     void (*kern)(const ScanArgs) = pl.chain > 1 ? (vec ? m2d_bwd_kernel<io_t, true, true> : m2d_bwd_kernel<io_t, false, true>)
                                                 : (vec ? m2d_bwd_kernel<io_t, true, false> : m2d_bwd_kernel<io_t, false, false>);
-    if (pl.smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
-        return M2D_ERR_LAUNCH;
-    if (a.chain > 1) {
-        // cooperative launch: every CTA of a chain must be resident (see the forward launch)
-        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)block.x, pl.smem) != cudaSuccess || per_sm < 1)
-            return M2D_ERR_LAUNCH;
-        const long long fit = (long long)per_sm * sm_count() / ((long long)pl.grid_x * pl.groups);
-        if (fit < a.chain) a.chain = fit < 1 ? 1 : (int)fit;
-        for (;;) {
-            dim3 grid(pl.grid_x * a.chain, pl.groups);
-            void* args[] = {&a};
-            const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), grid, block, args, pl.smem, st);
-            if (e == cudaSuccess) break;
-            cudaGetLastError();
-            if (e != cudaErrorCooperativeLaunchTooLarge || a.chain == 1) return M2D_ERR_LAUNCH;
-            a.chain = a.chain > 2 ? a.chain - a.chain / 4 - 1 : 1;
-        }
-    } else {
-        dim3 grid(pl.grid_x, pl.groups);
-        kern<<<grid, block, pl.smem, st>>>(a);
-        if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
-    }
+    const int rc = launch_sweep_kernel(kern, a, pl, d->W, st);
+    if (rc != M2D_OK) return rc;
     if (d->dtype != M2D_F32) {
         const int fin_blocks = (int)((npn + 255) / 256 < 148 * 8 ? (npn + 255) / 256 : 148 * 8);
         m2d_bwd_finalize<io_t><<<fin_blocks, 256, 0, st>>>(a.accBT, static_cast<io_t*>(d->d_BT), static_cast<io_t*>(d->d_BL),
@@ -265,10 +231,12 @@ extern "C" uint64_t m2d_scan_bwd_workspace(const m2d_scan_desc* d) {
 
 extern "C" int64_t m2d_scan_bwd_status_offset(const m2d_scan_desc* d) {
     if (m2d::check_desc(d, true, false) != M2D_OK) return -1;
-    const m2d::Plan pl = m2d::plan_bwd(d);
-    if (pl.chain <= 1) return -1;
-    const m2d::BwdLayout L = m2d::bwd_layout(d, pl);
-    return (int64_t)(L.counters + 2 * (size_t)d->B * pl.groups * pl.nbands * sizeof(int));
+    return 0;
+}
+
+extern "C" int m2d_scan_bwd_chain(const m2d_scan_desc* d) {
+    if (m2d::check_desc(d, true, false) != M2D_OK) return 0;
+    return m2d::plan_bwd(d).chain;
 }
 
 extern "C" int m2d_scan_bwd(const m2d_scan_desc* d, void* stream) {

@@ -1,6 +1,5 @@
 // Forward entry point of the wavefront scan: one fused kernel, y written directly.
-#include "plan.cuh"
-#include "sweep_fwd.cuh"
+#include "launch.cuh"
 
 namespace m2d {
 
@@ -34,29 +33,21 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
 template <typename io_t>
 static int launch_fwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStream_t st) {
     FwdArgs a;
-    a.B = d->B; a.H = d->H; a.W = d->W; a.E = d->E; a.N = d->N;
-    a.dir = (d->flags & M2D_SCAN_REVERSE) ? -1 : 1;
-    a.x = d->x; a.dT = d->dT; a.dL = d->dL; a.AT = d->AT; a.AL = d->AL;
-    a.BT = d->BT; a.BL = d->BL; a.C = d->C; a.D = d->D;
-    a.pBT = d->BT_pitch; a.pBL = d->BL_pitch; a.pC = d->C_pitch;
+    fill_common_args(a, d, pl);
+    char* ws = static_cast<char*>(d->workspace);
     a.y = d->y;
-    a.gy = nullptr;
-    a.ring = static_cast<float4*>(d->workspace);
-    a.hs = nullptr;
-    a.Rb = pl.Rb; a.nbands = pl.nbands;
-    a.chain = pl.chain;
-    a.bnd = nullptr; a.progress = nullptr; a.status = nullptr;
+    a.status = reinterpret_cast<int*>(ws);
+    a.ring = reinterpret_cast<float4*>(ws + kStatusBytes);
+    size_t zero_bytes = sizeof(int);
     if (pl.chain > 1) {
-        // workspace = [boundary rows of every band][column counters + status word]
-        char* ws = static_cast<char*>(d->workspace);
+        // workspace = [status word][column counters][boundary rows of every band]: one memset clears the
+        // status word and the counters
         const size_t nband = (size_t)d->B * pl.groups * pl.nbands;
-        const size_t bnd_bytes = align256(nband * d->W * kSlotF4 * sizeof(float4));
-        a.bnd = reinterpret_cast<float4*>(ws);
-        a.progress = reinterpret_cast<int*>(ws + bnd_bytes);
-        a.status = a.progress + nband;
-        if (cudaMemsetAsync(a.progress, 0, (nband + 1) * sizeof(int), st) != cudaSuccess) return M2D_ERR_LAUNCH;
+        a.progress = reinterpret_cast<int*>(ws + kStatusBytes);
+        a.bnd = reinterpret_cast<float4*>(ws + kStatusBytes + align256(nband * sizeof(int)));
+        zero_bytes = kStatusBytes + nband * sizeof(int);
     }
-    dim3 block(pl.warps * 32);
+    if (cudaMemsetAsync(ws, 0, zero_bytes, st) != cudaSuccess) return M2D_ERR_LAUNCH;
     void (*kern)(const FwdArgs);
     if (pl.cb == 2) {
         kern = pl.chain > 1 ? (vec ? m2d_fwd_kernel<io_t, true, true, 2> : m2d_fwd_kernel<io_t, false, true, 2>)
@@ -65,32 +56,7 @@ static int launch_fwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
         kern = pl.chain > 1 ? (vec ? m2d_fwd_kernel<io_t, true, true, 1> : m2d_fwd_kernel<io_t, false, true, 1>)
                             : (vec ? m2d_fwd_kernel<io_t, true, false, 1> : m2d_fwd_kernel<io_t, false, false, 1>);
     }
-    if (pl.smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
-        return M2D_ERR_LAUNCH;
-    if (a.chain > 1) {
-        // CTAs of a chain wait on one another, so every CTA of the launch must be resident at the same
-        // time.  A cooperative launch guarantees that or fails cleanly; the chain is shortened until
-        // the device accepts it (the workspace layout does not depend on the chain length).
-        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)block.x, pl.smem) != cudaSuccess || per_sm < 1)
-            return M2D_ERR_LAUNCH;
-        const long long fit = (long long)per_sm * sm_count() / ((long long)pl.grid_x * pl.groups);
-        if (fit < a.chain) a.chain = fit < 1 ? 1 : (int)fit;
-        for (;;) {
-            dim3 grid(pl.grid_x * a.chain, pl.groups);
-            void* args[] = {&a};
-            const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), grid, block, args, pl.smem, st);
-            if (e == cudaSuccess) return M2D_OK;
-            cudaGetLastError();
-            if (e != cudaErrorCooperativeLaunchTooLarge || a.chain == 1) return M2D_ERR_LAUNCH;
-            a.chain = a.chain > 2 ? a.chain - a.chain / 4 - 1 : 1;
-        }
-    }
-    dim3 grid(pl.grid_x, pl.groups);
-    kern<<<grid, block, pl.smem, st>>>(a);
-    return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
+    return launch_sweep_kernel(kern, a, pl, (d->W + pl.cb - 1) / pl.cb, st);
 }
 
 }  // namespace m2d
@@ -102,10 +68,17 @@ extern "C" uint64_t m2d_scan_fwd_workspace(const m2d_scan_desc* d) {
 
 extern "C" int64_t m2d_scan_fwd_status_offset(const m2d_scan_desc* d) {
     if (m2d::check_desc(d, false, false) != M2D_OK) return -1;
-    const m2d::Plan pl = m2d::plan_fwd(d);
-    if (pl.chain <= 1) return -1;
-    const size_t nband = (size_t)d->B * pl.groups * pl.nbands;
-    return (int64_t)(m2d::align256(nband * d->W * m2d::kSlotF4 * sizeof(float4)) + nband * sizeof(int));
+    return 0;
+}
+
+extern "C" int m2d_scan_fwd_chain(const m2d_scan_desc* d) {
+    if (m2d::check_desc(d, false, false) != M2D_OK) return 0;
+    return m2d::plan_fwd(d).chain;
+}
+
+extern "C" int m2d_scan_chain_bound(int want, int nbands, int steps_per_row, int rows_per_band) {
+    if (nbands < 1 || steps_per_row < 1 || rows_per_band < 1) return 0;
+    return m2d::bound_chain(want, nbands, steps_per_row, rows_per_band);
 }
 
 extern "C" int m2d_scan_fwd(const m2d_scan_desc* d, void* stream) {
@@ -113,7 +86,7 @@ extern "C" int m2d_scan_fwd(const m2d_scan_desc* d, void* stream) {
     if (rc != M2D_OK) return rc;
     if (!d->y) return M2D_ERR_NULL;
     const m2d::Plan pl = m2d::plan_fwd(d);
-    if (pl.scratch > 0 && (!d->workspace || d->workspace_bytes < pl.scratch || (reinterpret_cast<uintptr_t>(d->workspace) & 255)))
+    if (!d->workspace || d->workspace_bytes < pl.scratch || (reinterpret_cast<uintptr_t>(d->workspace) & 255))
         return M2D_ERR_WORKSPACE;
     const bool vec = m2d::vector_ok(d, false);
     cudaStream_t st = static_cast<cudaStream_t>(stream);

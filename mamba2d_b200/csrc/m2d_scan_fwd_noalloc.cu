@@ -13,18 +13,18 @@
 //   - every GPU on which this library is loaded holds M2D_NOALLOC_SCRATCH_BYTES (32 MiB) of
 //     device memory from load until the process exits;
 //   - problems whose ring would not fit are rejected with M2D_ERR_TOO_LARGE;
-//   - all calls on one device share the one array.  Nothing in it has to start at zero (every slot
-//     is written before it is read within a call, and what an earlier call left behind is never
-//     read), but two calls that overlap in time on the same GPU -- different streams, or different
-//     host threads -- would overwrite each other's slots and produce wrong results.  Serialise
-//     them (one stream, or events between streams);
+//   - all calls on one device share the one array.  Only its first word (the status word the
+//     kernels share with the regular entry point's workspace layout) has to start at zero, and the
+//     call clears it itself; every other slot is written before it is read within a call, and what
+//     an earlier call left behind is never read.  But two calls that overlap in time on the same
+//     GPU -- different streams, or different host threads -- would overwrite each other's slots
+//     and produce wrong results.  Serialise them (one stream, or events between streams);
 //   - the first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress) and caches it; make that first call before starting any stream
 //     capture on that device.
 #include <mutex>
 
-#include "plan.cuh"
-#include "sweep_fwd.cuh"
+#include "launch.cuh"
 
 namespace m2d {
 
@@ -75,27 +75,26 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_noalloc_kernel(const ScanArgs 
 }
 
 template <typename io_t>
-static int launch_noalloc(const m2d_scan_desc* d, const Plan& pl, bool vec, float4* ring, cudaStream_t st) {
-    ScanArgs a = {};
-    a.B = d->B; a.H = d->H; a.W = d->W; a.E = d->E; a.N = d->N;
-    a.dir = (d->flags & M2D_SCAN_REVERSE) ? -1 : 1;
-    a.x = d->x; a.dT = d->dT; a.dL = d->dL; a.AT = d->AT; a.AL = d->AL;
-    a.BT = d->BT; a.BL = d->BL; a.C = d->C; a.D = d->D;
-    a.pBT = d->BT_pitch; a.pBL = d->BL_pitch; a.pC = d->C_pitch;
+static int launch_noalloc(const m2d_scan_desc* d, const Plan& pl, bool vec, float4* scratch, cudaStream_t st) {
+    ScanArgs a;
+    fill_common_args(a, d, pl);
     a.y = d->y;
-    a.ring = ring;
-    a.Rb = pl.Rb; a.nbands = pl.nbands;
+    // same layout as a caller's workspace: [status word][per-CTA rings]
+    char* base = reinterpret_cast<char*>(scratch);
+    a.status = reinterpret_cast<int*>(base);
+    a.ring = reinterpret_cast<float4*>(base + kStatusBytes);
     a.chain = 1;
-    dim3 grid(pl.grid_x, pl.groups), block(pl.warps * 32);
-    auto kern = vec ? m2d_fwd_noalloc_kernel<io_t, true> : m2d_fwd_noalloc_kernel<io_t, false>;
-    if (pl.smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
-        return M2D_ERR_LAUNCH;
-    kern<<<grid, block, pl.smem, st>>>(a);
-    return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
+    if (cudaMemsetAsync(base, 0, sizeof(int), st) != cudaSuccess) return M2D_ERR_LAUNCH;
+    void (*kern)(const ScanArgs) = vec ? m2d_fwd_noalloc_kernel<io_t, true> : m2d_fwd_noalloc_kernel<io_t, false>;
+    return launch_sweep_kernel(kern, a, pl, d->W, st);
 }
 
 }  // namespace m2d
+
+extern "C" uint64_t m2d_scan_fwd_noalloc_need(const m2d_scan_desc* d) {
+    if (m2d::check_desc(d, false, false) != M2D_OK) return 0;
+    return m2d::plan_fwd(d, false, false).scratch;
+}
 
 extern "C" int m2d_scan_fwd_noalloc(const m2d_scan_desc* d, void* stream) {
     int rc = m2d::check_desc(d, false, true);

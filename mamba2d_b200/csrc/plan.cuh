@@ -1,6 +1,8 @@
 // Host-side descriptor validation and launch planning (header-only, used by both entry points).
 #pragma once
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace m2d {
@@ -14,11 +16,21 @@ inline int sm_count() {
     return n;
 }
 
+// Test hooks in desc->flags are honoured only when the environment asks for them.
+inline bool test_hooks_enabled() {
+    const char* e = getenv("M2D_TEST_HOOKS");
+    return e && e[0] == '1';
+}
+
 inline int check_desc(const m2d_scan_desc* d, bool bwd, bool need_ptrs) {
     if (!d) return M2D_ERR_NULL;
     if (d->struct_bytes != sizeof(m2d_scan_desc)) return M2D_ERR_ABI;
     if (d->dtype != M2D_F32 && d->dtype != M2D_BF16) return M2D_ERR_DTYPE;
-    if (d->flags & ~M2D_SCAN_REVERSE) return M2D_ERR_FLAGS;
+    {
+        unsigned known = M2D_SCAN_REVERSE;
+        if (test_hooks_enabled()) known |= M2D_SCAN_TEST_WITHHOLD;
+        if (d->flags & ~known) return M2D_ERR_FLAGS;
+    }
     if (d->B < 1 || d->E < 1 || d->N < 1 || d->H < 2 || d->W < 2) return M2D_ERR_SHAPE;
     if (d->N > kMaxN) return M2D_ERR_UNSUPPORTED_N;
     if (d->BT_pitch < d->N || d->BL_pitch < d->N || d->C_pitch < d->N) return M2D_ERR_PITCH;
@@ -113,36 +125,43 @@ inline Plan plan_best(const m2d_scan_desc* d, int max_warps, int warps_per_sm, i
 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+// Scratch layout shared by every entry point: [status word, 256 bytes][the rest].
+constexpr size_t kStatusBytes = 256;
+
+// CTAs per image that a launch may use.  When a CTA owns more than one band the chain closes into a
+// ring: its first warp enters the second band while (through the per-step block barrier) the warps
+// behind it are still up to Rb-1 steps back in the first, and so on around the ring.  The ring must
+// be shorter than one row of steps, or the head would wait on data that waits on the head.  `want`
+// is the chain the resident CTA slots allow; `steps_per_row` the steps a warp needs for one row.
+// Every place that picks or shortens a chain goes through this rule.
+inline int bound_chain(long long want, int nbands, int steps_per_row, int Rb) {
+    if (want > nbands) want = nbands;
+    if (want < nbands) {
+        const long long lim = steps_per_row / Rb - 1;
+        if (want > lim) want = lim;
+    }
+    return want < 1 ? 1 : (int)want;
+}
+
 inline Plan plan_fwd(const m2d_scan_desc* d, bool allow_chain = true, bool allow_cb = true) {
     Plan p = plan_best(d, 8, 16, 1);
     // Few images on a large map: give every image a chain of CTAs, each owning every chain-th band,
     // so that the bands of one image run as a pipeline across SMs.  All CTAs must be resident.
     const long long slots = (long long)(16 / p.warps > 0 ? 16 / p.warps : 1) * sm_count();
     const long long ctas = (long long)p.grid_x * p.groups;
-    if (allow_chain && p.nbands > 1 && ctas * 2 <= slots) {
-        long long c = slots / ctas;
-        if (c > p.nbands) c = p.nbands;
-        // When a CTA owns more than one band the chain closes into a ring: its first warp enters the
-        // second band while (through the per-step block barrier) the warps behind it are still up to
-        // Rb-1 steps back in the first, and so on around the ring.  The ring must be shorter than
-        // one row of steps, or the head would wait on data that waits on the head.
-        const int nch = (d->W + p.cb - 1) / p.cb;
-        if (c < p.nbands) {
-            const long long lim = nch / p.Rb - 1;
-            if (c > lim) c = lim;
-        }
-        p.chain = c < 1 ? 1 : (int)c;
-    }
+    if (allow_chain && p.nbands > 1 && ctas * 2 <= slots)
+        p.chain = bound_chain(slots / ctas, p.nbands, (d->W + p.cb - 1) / p.cb, p.Rb);
     if (p.chain == 1 && allow_cb && d->W >= 24) {
         // batch mode: two cells per step where rows are long enough for the band hand-off to stay
         // a step ahead (measured 7 % faster at 56x56 and 28x28; chained launches prefer finer steps)
         p = plan_best(d, 8, 16, 2);
     }
+    p.scratch = kStatusBytes;
     if (p.chain > 1) {
         const size_t nband = (size_t)d->B * p.groups * p.nbands;
-        p.scratch = align256(nband * d->W * kSlotF4 * sizeof(float4)) + align256((nband + 1) * sizeof(int));
+        p.scratch += align256(nband * sizeof(int)) + align256(nband * d->W * kSlotF4 * sizeof(float4));
     } else if (p.nbands > 1) {
-        p.scratch = align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
+        p.scratch += align256((size_t)p.grid_x * p.groups * d->W * kSlotF4 * sizeof(float4));
     }
     return p;
 }

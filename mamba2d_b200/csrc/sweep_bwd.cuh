@@ -46,7 +46,6 @@ struct RevRun {
     const float4* phl;      // state record of h[i][j-1] for the cell being staged
     int pixc, jc, qc;       // compute side
     bool row_c, push_c, bottom_c, row0_c;
-    float cfac, mT, mL, offT, offL;   // constants of the current cell class
 };
 
 // One CTA's adjoint sweep over image `b`.  dAT/dAL/dD accumulate across calls.
@@ -102,7 +101,6 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
     st.row_l = st.pull_l = st.top_l = st.row_c = st.push_c = st.bottom_c = st.row0_c = false;
     st.phl = nullptr;
     st.seen = 0; st.pull = ring; st.pcount = nullptr; st.push = ring; st.ccount = nullptr;
-    st.cfac = st.mT = st.mL = st.offT = st.offL = 0.f;
 
     // One state-record block, global -> shared (2 KiB of fp32 states or 1 KiB of bf16 states).
     auto copy_block = [&](bool on, unsigned dst, const float4* src) {
@@ -149,7 +147,7 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
         }
         const int j = W - 1 - st.jl;
         if (chain > 1 && st.pull_l && st.seen < st.jl + 1)
-            st.seen = wait_columns(st.pcount, st.jl + 1, a.status, lane);
+            st.seen = wait_columns(st.pcount, st.jl + 1, a.status, a.wait_limit);
         if (st.row_l) {
             char* stg = stage + par * kStageBytes;
             if (VEC) {
@@ -191,12 +189,6 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
             st.bottom_c = (i + 1 >= H);
             st.push_c = st.row_c && (r == 0) && (q > 0);
             st.pixc = scan_pixel(a, b, i, W - 1);
-            // columns j > 0: interior unless on row 0
-            st.cfac = st.row0_c ? 1.f : 0.5f;
-            st.mT = st.row0_c ? 0.f : 1.f;
-            st.mL = 1.f;
-            st.offT = st.row0_c ? ninf : 0.f;
-            st.offL = 0.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -204,13 +196,22 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
         }
         if (st.row_c) {
             const int j = W - 1 - st.jc;
-            if (j == 0) {   // column 0: no averaging, no left neighbour; the left input term exists only on row 0
-                st.cfac = 1.f;
-                st.mL = st.row0_c ? 1.f : 0.f;
-                st.offL = ninf;
+          auto cell = [&](auto tag) {
+            constexpr bool INTERIOR = decltype(tag)::value;
+            // cells inside the map (row > 0, column > 0) have constant weights; row 0 and column 0 take
+            // the generic path, where a missing neighbour's state is taken as zero instead of being read
+            float cfac, mT, mL, offT, offL;
+            if (INTERIOR) {
+                cfac = 0.5f; mT = 1.f; mL = 1.f; offT = 0.f; offL = 0.f;
+            } else {
+                const bool first = (j == 0);   // column 0: no averaging, no left neighbour; the left input term exists only on row 0
+                cfac = (st.row0_c || first) ? 1.f : 0.5f;
+                mT = st.row0_c ? 0.f : 1.f;
+                mL = (first && !st.row0_c) ? 0.f : 1.f;
+                offT = st.row0_c ? ninf : 0.f;
+                offL = first ? ninf : 0.f;
             }
-            const float cfac = st.cfac, mT = st.mT, mL = st.mL;
-            const float2 offT2 = make_float2(st.offT, st.offT), offL2 = make_float2(st.offL, st.offL);
+            const float2 offT2 = make_float2(offT, offT), offL2 = make_float2(offL, offL);
             const char* stg = stage + (par ^ 1) * kStageBytes;
             const float4 vx = unstage4<io_t>(stg + cq * 16);
             const float4 vdT = unstage4<io_t>(stg + (8 + cq) * 16);
@@ -232,8 +233,8 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
             float o_dT[4], o_dL[4], o_dx[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const float4 hl4 = block_states(h_own + (par ^ 1) * kSlotF4, c);
-                const float4 ht4 = block_states(h_up + (par ^ 1) * kSlotF4, c);
+                const float4 hl4 = (INTERIOR || j > 0) ? block_states(h_own + (par ^ 1) * kSlotF4, c) : zero4;
+                const float4 ht4 = (INTERIOR || !st.row0_c) ? block_states(h_up + (par ^ 1) * kSlotF4, c) : zero4;
                 const float4 pd4 = st.bottom_c ? zero4 : my[(par ^ 1) * kSlotF4 + c * 32];
                 const float hls[4] = {hl4.x, hl4.y, hl4.z, hl4.w};
                 const float hts[4] = {ht4.x, ht4.y, ht4.z, ht4.w};
@@ -248,8 +249,8 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
 #pragma unroll
                 for (int n = 0; n < 4; n += 2) {
                     const float2 aT = make_float2(aT2c[n], aT2c[n + 1]), aL = make_float2(aL2c[n], aL2c[n + 1]);
-                    const float2 argT = __ffma2_rn(make_float2(dTs[c], dTs[c]), aT, offT2);
-                    const float2 argL = __ffma2_rn(make_float2(dLs[c], dLs[c]), aL, offL2);
+                    const float2 argT = INTERIOR ? __fmul2_rn(make_float2(dTs[c], dTs[c]), aT) : __ffma2_rn(make_float2(dTs[c], dTs[c]), aT, offT2);
+                    const float2 argL = INTERIOR ? __fmul2_rn(make_float2(dLs[c], dLs[c]), aL) : __ffma2_rn(make_float2(dLs[c], dLs[c]), aL, offL2);
                     const float2 gT = make_float2(ex2(argT.x), ex2(argT.y));
                     const float2 gL = make_float2(ex2(argL.x), ex2(argL.y));
                     const float2 in = __fmul2_rn(make_float2(cfac, cfac),
@@ -276,17 +277,22 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 my[kSlotPair + par * kSlotF4 + c * 32] = pT4;
                 stcg_if(st.push_c, st.push + j * kSlotF4 + c * 32, pT4);
                 const float qT = qT2.x + qT2.y, qL = qL2.x + qL2.y, sT = sT2.x + sT2.y, sL = sL2.x + sL2.y;
-                o_dT[c] = fmaf(qT, kLn2, mT * xs[c] * sT);
-                o_dL[c] = fmaf(qL, kLn2, mL * xs[c] * sL);
-                o_dx[c] = fmaf(mT * dTs[c], sT, mL * dLs[c] * sL);
+                if (INTERIOR) {
+                    o_dT[c] = fmaf(qT, kLn2, xs[c] * sT);
+                    o_dL[c] = fmaf(qL, kLn2, xs[c] * sL);
+                    o_dx[c] = fmaf(dTs[c], sT, dLs[c] * sL);
+                } else {
+                    o_dT[c] = fmaf(qT, kLn2, mT * xs[c] * sT);
+                    o_dL[c] = fmaf(qL, kLn2, mL * xs[c] * sL);
+                    o_dx[c] = fmaf(mT * dTs[c], sT, mL * dLs[c] * sL);
+                }
                 dD[c] = fmaf(gys[c], xs[c], dD[c]);
             }
 
             if (chain > 1 && st.push_c) {
                 // publish the column (columns are produced right to left): data first, then the counter
-                __threadfence();
                 __syncwarp();
-                if (lane == 0) *reinterpret_cast<volatile int*>(st.ccount) = st.jc + 1;
+                if (lane == 0) st_release_gpu(st.ccount, st.jc + 1);
             }
 
             // sums over states: 2-step exchange over the nq lanes; lane l ends with channel l of the group
@@ -320,6 +326,9 @@ __device__ __forceinline__ void reverse_sweep(const ScanArgs& a, float4* handoff
                 // this lane now owns array (hi16 ? d_BL : d_BT), state n0 + 2*hi8 + hi4
                 if (db_lane) atomicAdd(db_acc + ((long long)st.pixc * a.N + db_n), v);
             }
+          };
+            if (st.row0_c || j == 0) cell(std::false_type{});
+            else cell(std::true_type{});
             st.pixc -= a.dir;
         }
         if (++st.jc == W) { st.jc = 0; ++st.qc; }

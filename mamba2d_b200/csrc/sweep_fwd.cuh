@@ -22,6 +22,8 @@
 // (load / compute) that is recomputed only at the start of a row.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace m2d {
@@ -40,7 +42,9 @@ struct ScanArgs {
     int chain;                // 1 = one CTA per image
     float4* bnd;              // [image][group][band][W][4][32] float4
     int* progress;            // [image][group][band]: columns of the band's last row published so far
-    int* status;              // nonzero if a wait on `progress` gave up (results are then invalid)
+    int* status;              // nonzero if a wait on `progress` gave up (results are then invalid); never null
+    int wait_limit;           // polls before such a wait gives up
+    int withhold;             // test hook: the first band of image 0 never publishes its column counter
     // ---- backward only ----
     const void* gy;
     float4* hs;               // full state record: [b][group][H*W] blocks; a block is [4][32] float4 (fp32 I/O)
@@ -95,28 +99,25 @@ struct CellIn {
     float4 gy;   // only loaded by the backward sweeps
 };
 
-// Bounded wait of a consumer warp on a producer's column counter (another CTA).  Returns the value
-// seen; after kWaitPolls unsuccessful polls it records the failure in *status and gives up, so a
-// kernel can never spin forever.
+// Bounded wait of a consumer warp on a producer's column counter (another CTA).  Every lane polls
+// with an acquire load (one request per warp), so each lane's later reads of the published data are
+// ordered after the counter it saw.  Returns the value seen; after `wait_limit` unsuccessful polls,
+// or as soon as any wait of the launch has given up, it records the failure in the status word and
+// returns a huge value (the caller then stops waiting for the rest of the row), so a kernel can
+// never spin forever.
 constexpr int kWaitPolls = 1 << 22;
-__device__ __forceinline__ int wait_columns(const int* counter, int need, int* status, int lane) {
-    int seen = 0;
-    if (lane == 0) {
-        const volatile int* c = counter;
-        int polls = 0;
-        seen = *c;
-        while (seen < need) {
-            if (++polls > kWaitPolls || *reinterpret_cast<volatile int*>(status) != 0) {
-                atomicExch(status, 1);
-                seen = 0x7fffffff;   // stop waiting for the rest of the kernel
-                break;
-            }
-            __nanosleep(64);
-            seen = *c;
+__device__ __forceinline__ int wait_columns(const int* counter, int need, int* status, int limit) {
+    int seen = ld_acquire_gpu(counter);
+    int polls = 0;
+    while (seen < need) {
+        if (++polls > limit || *reinterpret_cast<volatile int*>(status) != 0) {
+            atomicExch(status, 1);
+            return 0x7fffffff;
         }
-        __threadfence();   // order the data reads after the counter read
+        __nanosleep(64);
+        seen = ld_acquire_gpu(counter);
     }
-    return __shfl_sync(0xffffffffu, seen, 0);
+    return seen;
 }
 
 // Per-warp running state of a forward sweep.  Addresses are rebuilt every step from a running 32-bit
@@ -134,6 +135,7 @@ struct FwdRun {
     float4* phs;            // state record of the current cell (recompute sweep only)
     int jc, qc, bic;
     bool row_c, row0_c, push_c;
+    bool silent_c;          // test hook: this band does not publish its column counter
     float4* push;           // where this band's last row goes
     int* ccount;            // its column counter (chained CTAs)
 };
@@ -193,7 +195,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
     FwdRun st;
     st.jl = st.ql = st.bil = 0;
     st.jc = st.qc = st.bic = 0;
-    st.row_l = st.pull_l = st.row_c = st.row0_c = st.push_c = false;
+    st.row_l = st.pull_l = st.row_c = st.row0_c = st.push_c = st.silent_c = false;
     st.pixl = st.pixc = 0;
     st.phs = nullptr;
     st.seen = 0; st.pull = ring; st.pcount = nullptr; st.push = ring; st.ccount = nullptr;
@@ -217,7 +219,7 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
         const int col0 = st.jl * CB;
         if (chain > 1 && st.pull_l) {
             const int need = min(col0 + CB, W);
-            if (st.seen < need) st.seen = wait_columns(st.pcount, need, a.status, lane);
+            if (st.seen < need) st.seen = wait_columns(st.pcount, need, a.status, a.wait_limit);
         }
         if (st.row_l) {
 #pragma unroll
@@ -263,25 +265,42 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                 const size_t band = ((size_t)b * groups + g) * nbands + q;
                 st.push = a.bnd + band * W * kSlotF4 + lane;
                 st.ccount = a.progress + band;
+                st.silent_c = a.withhold != 0 && b == 0 && q == 0;
             }
             st.pixc = scan_pixel(a, b, i, 0);
+            // a fresh row starts from no left neighbour: nothing of the previous row, band or image is
+            // carried into it (the gate of a missing neighbour is zero, but zero times a diverged
+            // state would not be)
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int n = 0; n < 4; ++n) h[c][n] = 0.f;
             if (STORE_HS) st.phs = a.hs + (((size_t)b * groups + g) * H * W + (size_t)i * W) * HsBlock<io_t>::f4 + lane;
         }
         if (st.row_c) {
             const int col0 = st.jc * CB;
-#pragma unroll
-            for (int cc = 0; cc < CB; ++cc) {
-                const int col = col0 + cc;
-                if (CB == 1 || col < W) {
-                    const bool first = (col == 0);
-                    const float wT = st.row0_c ? 0.f : (first ? 1.f : 0.5f);
-                    const float wL = first ? (st.row0_c ? 1.f : 0.f) : (st.row0_c ? 1.f : 0.5f);
-                    const float offT = st.row0_c ? ninf : (first ? 0.f : -1.f);
-                    const float offL = first ? ninf : (st.row0_c ? 0.f : -1.f);
+            auto cell = [&](auto tag, const int cc, const int col) {
+                constexpr bool INTERIOR = decltype(tag)::value;
+                    // cells inside the map (row > 0, column > 0) have constant weights; row 0 and
+                    // column 0 take the generic path, where a missing neighbour's state is taken as
+                    // zero instead of being read
+                    float wT, wL, offT, offL;
+                    if (INTERIOR) {
+                        wT = 0.5f; wL = 0.5f; offT = -1.f; offL = -1.f;
+                    } else {
+                        const bool first = (col == 0);
+                        wT = st.row0_c ? 0.f : (first ? 1.f : 0.5f);
+                        wL = first ? (st.row0_c ? 1.f : 0.f) : (st.row0_c ? 1.f : 0.5f);
+                        offT = st.row0_c ? ninf : (first ? 0.f : -1.f);
+                        offL = first ? ninf : (st.row0_c ? 0.f : -1.f);
+                    }
 
                     float4 top[4];
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) top[k] = my[((par ^ 1) * CB + cc) * kSlotF4 + k * 32];
+                    for (int k = 0; k < 4; ++k) {
+                        top[k] = my[((par ^ 1) * CB + cc) * kSlotF4 + k * 32];
+                        if (!INTERIOR && st.row0_c) top[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
                     CellIn cur;   // staged during the previous step
                     {
                         const char* stg = stage + ((par ^ 1) * CB + cc) * kStageBytes;
@@ -369,13 +388,20 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                         if (y_lane) store1(static_cast<io_t*>(a.y), st.pixc * E + g * kGroup + lane, fmaf(sel4(cur.x, nq), D_own, ysum));
                     }
                     st.pixc += a.dir;
+            };
+#pragma unroll
+            for (int cc = 0; cc < CB; ++cc) {
+                const int col = col0 + cc;
+                if (CB == 1 || col < W) {
+                    if (st.row0_c || col == 0) cell(std::false_type{}, cc, col);
+                    else cell(std::true_type{}, cc, col);
                 }
             }
             if (chain > 1 && st.push_c) {
-                // publish the chunk's columns: data first, then the counter
-                __threadfence();
+                // publish the chunk's columns: data first, then the counter.  __syncwarp orders the other
+                // lanes' stores before lane 0's release store, which makes them visible with the counter.
                 __syncwarp();
-                if (lane == 0) *reinterpret_cast<volatile int*>(st.ccount) = min(col0 + CB, W);
+                if (lane == 0 && !st.silent_c) st_release_gpu(st.ccount, min(col0 + CB, W));
             }
         }
         if (++st.jc == nch) {

@@ -33,7 +33,27 @@ from . import _lib
 __all__ = ["wavefront_scan_cuda", "wf_cuda_fn_pr", "wf_cuda_fn_fr", "proj_params", "scan_fwd", "scan_bwd"]
 
 _DTYPES = {torch.float32: _lib.M2D_F32, torch.bfloat16: _lib.M2D_BF16}
-_CHECK_STATUS = os.environ.get("M2D_CHECK_STATUS", "0") == "1"
+# When to read the status word a launch leaves in its workspace (reading it synchronises):
+# "1" after every call, "0" never, anything else (the default) only after launches that run several
+# CTAs per image -- the ones whose bounded waits cross CTAs -- and never during stream capture.
+_CHECK_STATUS = os.environ.get("M2D_CHECK_STATUS", "auto")
+
+
+def _check_status(kind, d, ws):
+    """Raise if a bounded wait inside the launch gave up (the results are then void)."""
+    if _CHECK_STATUS == "0" or torch.cuda.is_current_stream_capturing():
+        return
+    L = _lib.lib()
+    if _CHECK_STATUS != "1" and getattr(L, f"m2d_scan_{kind}_chain")(ctypes.byref(d)) <= 1:
+        return
+    off = getattr(L, f"m2d_scan_{kind}_status_offset")(ctypes.byref(d))
+    if off >= 0 and _status_word(ws, off) != 0:
+        what = "output is" if kind == "fwd" else "gradients are"
+        raise RuntimeError(f"m2d_scan_{kind}: a wait between row-warps or CTAs timed out; the {what} invalid")
+
+
+def _status_word(ws, off):
+    return int(ws[off:off + 4].view(torch.int32).item())      # .item() synchronises
 
 
 # -----------------------------------------------------------------------------
@@ -114,8 +134,9 @@ def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
     ``scan_fwd(*[t.flip(1, 2) for t in pixel_tensors], ...).flip(1, 2)`` without any copy.
 
     With few images on a large map the kernel runs several CTAs per image that wait on one another
-    with bounded polling; set ``M2D_CHECK_STATUS=1`` to synchronise after the call and raise if
-    such a wait ever gave up (status word in the workspace, see m2d_scan_fwd_status_offset)."""
+    with bounded polling.  After such a launch the wrapper synchronises and raises if a wait gave
+    up (status word in the workspace, see m2d_scan_fwd_status_offset); ``M2D_CHECK_STATUS=1``
+    extends that check to every launch, ``M2D_CHECK_STATUS=0`` switches it off."""
     _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
     L = _lib.lib()
     with torch.cuda.device(x.device):
@@ -125,10 +146,7 @@ def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
         _workspace(d, L.m2d_scan_fwd_workspace(ctypes.byref(d)), x.device, keep)
         rc = L.m2d_scan_fwd(ctypes.byref(d), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     _lib.check(rc, "m2d_scan_fwd")
-    if _CHECK_STATUS:
-        off = L.m2d_scan_fwd_status_offset(ctypes.byref(d))
-        if off >= 0 and keep[-1][off:off + 4].view(torch.int32).item() != 0:      # .item() synchronises
-            raise RuntimeError("m2d_scan_fwd: a wait between CTAs of one image timed out; the output is invalid")
+    _check_status("fwd", d, keep[-1])
     return y
 
 
@@ -136,9 +154,9 @@ def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False
     """Fused backward with recomputation.  Returns the nine gradients
     (d_x, d_deltaT, d_deltaL, d_AT, d_AL, d_BT, d_BL, d_C, d_D), all in ``x.dtype``.
 
-    With ``shared_storage`` the six reduced gradients (d_AT ... d_D) are disjoint views of one
-    allocation, which lets the library zero them with one memset; the registered operator asks
-    for separate tensors, because operator outputs must not share storage."""
+    With ``shared_storage`` the reduced gradients are disjoint views of two allocations (per-pixel
+    and per-channel ones), which lets the library zero them with two memsets; the registered
+    operator asks for separate tensors, because operator outputs must not share storage."""
     B, H, W, E, N = _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output)
     L = _lib.lib()
     dev, dt = x.device, x.dtype
@@ -147,14 +165,17 @@ def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False
         gy = grad_output.contiguous()
         keep.append(gy)
         d.gy = gy.data_ptr()
-        # the six reduced gradients are carved out of one buffer in the order the library zeroes them
-        # (d_BT, d_BL, d_C, d_AT, d_AL, d_D): one memset instead of six
+        # the three per-pixel reduced gradients are carved out of one buffer and the three per-channel
+        # ones out of another, in the order the library zeroes them: two memsets instead of six.  (One
+        # buffer for all six would let the tiny d_D, which autograd may keep as D.grad, pin the
+        # large per-pixel storage until the gradients are cleared.)
         npn, en = B * H * W * N, E * N
-        flat = torch.empty(3 * npn + 2 * en + E, dtype=dt, device=dev) if shared_storage else None
-        if flat is not None:
-            d_BT, d_BL, d_C = (flat[k * npn:(k + 1) * npn].view(B, H, W, N) for k in range(3))
-            d_AT, d_AL = (flat[3 * npn + k * en:3 * npn + (k + 1) * en].view(E, N) for k in range(2))
-            d_D = flat[3 * npn + 2 * en:]
+        if shared_storage:
+            big = torch.empty(3 * npn, dtype=dt, device=dev)
+            small = torch.empty(2 * en + E, dtype=dt, device=dev)
+            d_BT, d_BL, d_C = (big[k * npn:(k + 1) * npn].view(B, H, W, N) for k in range(3))
+            d_AT, d_AL = (small[k * en:(k + 1) * en].view(E, N) for k in range(2))
+            d_D = small[2 * en:]
         else:
             d_BT, d_BL, d_C = (torch.empty((B, H, W, N), dtype=dt, device=dev) for _ in range(3))
             d_AT, d_AL = (torch.empty((E, N), dtype=dt, device=dev) for _ in range(2))
@@ -166,10 +187,7 @@ def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False
         _workspace(d, L.m2d_scan_bwd_workspace(ctypes.byref(d)), dev, keep)
         rc = L.m2d_scan_bwd(ctypes.byref(d), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     _lib.check(rc, "m2d_scan_bwd")
-    if _CHECK_STATUS:
-        off = L.m2d_scan_bwd_status_offset(ctypes.byref(d))
-        if off >= 0 and keep[-1][off:off + 4].view(torch.int32).item() != 0:
-            raise RuntimeError("m2d_scan_bwd: a wait between CTAs of one image timed out; the gradients are invalid")
+    _check_status("bwd", d, keep[-1])
     return outs
 
 

@@ -67,23 +67,61 @@ def test_descriptor_validation_without_a_device(L):
 
 
 def test_workspace_queries(L):
-    # one band (no more rows than a CTA has row-warps): the forward needs no scratch
-    assert L.m2d_scan_fwd_workspace(ctypes.byref(_desc(H=4))) == 0
+    # one band (no more rows than a CTA has row-warps): the forward needs the status word only
+    assert L.m2d_scan_fwd_workspace(ctypes.byref(_desc(H=4))) == 256
     # several bands: a per-CTA ring of W slots of 2 KiB
     d = _desc(B=128, H=56, W=56)
     ws = L.m2d_scan_fwd_workspace(ctypes.byref(d))
-    assert ws > 0 and ws % 256 == 0 and ws <= 128 * 2 * 56 * 2048
+    assert ws > 256 and ws % 256 == 0 and ws <= 256 + 128 * 2 * 56 * 2048
     # backward: state record B*groups*H*W*2 KiB plus accumulators
     wb = L.m2d_scan_bwd_workspace(ctypes.byref(d))
     assert wb >= 128 * 2 * 56 * 56 * 2048
     assert L.m2d_scan_fwd_workspace(ctypes.byref(_desc(H=1))) == 0    # invalid descriptor
 
 
-def test_status_offset_only_for_chained_problems(L):
-    assert L.m2d_scan_fwd_status_offset(ctypes.byref(_desc(B=128, H=56, W=56))) == -1      # enough images: one CTA each
+def test_status_word_and_chain_queries(L):
+    d = _desc(B=128, H=56, W=56)
+    assert L.m2d_scan_fwd_status_offset(ctypes.byref(d)) == 0
+    assert L.m2d_scan_bwd_status_offset(ctypes.byref(d)) == 0
+    assert L.m2d_scan_fwd_chain(ctypes.byref(d)) == 1 and L.m2d_scan_bwd_chain(ctypes.byref(d)) == 1   # enough images: one CTA each
     d = _desc(B=1, H=256, W=256)
-    off = L.m2d_scan_fwd_status_offset(ctypes.byref(d))
-    assert 0 < off < L.m2d_scan_fwd_workspace(ctypes.byref(d)) and off % 4 == 0
+    assert L.m2d_scan_fwd_chain(ctypes.byref(d)) > 1 and L.m2d_scan_bwd_chain(ctypes.byref(d)) > 1
+    assert L.m2d_scan_fwd_status_offset(ctypes.byref(_desc(H=1))) == -1 and L.m2d_scan_fwd_chain(ctypes.byref(_desc(H=1))) == 0
+    # more bands than resident CTAs: the chain closes into a ring, which must stay shorter than one
+    # row of steps (W / Rb - 1 with eight row-warps)
+    d = _desc(B=1, H=2400, W=24, E=32)
+    assert L.m2d_scan_fwd_chain(ctypes.byref(d)) == 24 // 8 - 1
+    d = _desc(B=1, H=2400, W=200, E=32)
+    assert L.m2d_scan_fwd_chain(ctypes.byref(d)) == 200 // 8 - 1
+
+
+def test_chain_bound_over_shrink_sequences(L):
+    """A planned chain and every chain a launch may fall back to obey the same rule: never more CTAs
+    than bands, and a chain that closes into a ring stays below one row of steps per band height."""
+    for nbands in (1, 2, 7, 10, 128, 300):
+        for steps in (2, 3, 12, 24, 56, 1024):
+            for rb in (1, 2, 6, 8):
+                if rb > steps:
+                    continue
+                want = 296
+                for _ in range(40):
+                    c = L.m2d_scan_chain_bound(want, nbands, steps, rb)
+                    assert 1 <= c <= nbands
+                    assert c == nbands or c == 1 or c <= steps // rb - 1
+                    assert c <= max(want, 1)
+                    if c == 1:
+                        break
+                    want = c - c // 4 - 1 if c > 2 else 1      # how a refused cooperative launch shrinks it
+                else:
+                    raise AssertionError("the shrink sequence did not reach 1")
+    assert L.m2d_scan_chain_bound(4, 0, 8, 2) == 0
+
+
+def test_test_hook_flag_needs_the_environment(L, monkeypatch):
+    monkeypatch.delenv("M2D_TEST_HOOKS", raising=False)
+    assert L.m2d_scan_fwd(ctypes.byref(_desc(flags=_lib.M2D_SCAN_TEST_WITHHOLD)), None) == -10
+    monkeypatch.setenv("M2D_TEST_HOOKS", "1")
+    assert L.m2d_scan_fwd(ctypes.byref(_desc(flags=_lib.M2D_SCAN_TEST_WITHHOLD)), None) == -1   # accepted: next check
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -61,3 +61,73 @@ def test_shard_bounds_tile_the_batch():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         shard_bounds(4, 2, 2)
+
+
+def _ddp_worker(rank, world, port, ret):
+    """Two ranks, each with half of the global batch, one optimiser step under DistributedDataParallel."""
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        model, x, labels = _tiny_classifier()
+        ddp = torch.nn.parallel.DistributedDataParallel(model)
+        from mamba2d_b200 import refmodel
+        opt = refmodel.make_optimizer(ddp, lr=1e-3)
+        n = x.shape[0] // world
+        loss = refmodel.train_step(ddp, opt, x[rank * n:(rank + 1) * n], labels[rank * n:(rank + 1) * n], micro_batch=1,
+                                   autocast_dtype=None)
+        ret[rank] = dict(loss=float(loss), params=[p.detach().clone().numpy() for p in model.parameters()])
+    finally:
+        dist.destroy_process_group()
+
+
+def _tiny_classifier():
+    """A four-stage classifier built from the reference's own classes (small widths, one block per
+    stage) with a naive PyTorch scan standing in for the kernels, and a seeded batch of 4 images."""
+    from mamba2d_b200 import refmodel
+    from oracle import torch_ref
+
+    def naive(x, *w, recomp="partial", scan_start="TL"):
+        if len(w) == 9:
+            *w, recomp = w
+        if scan_start == "BR":
+            return torch_ref.scan_from_weights(x.flip(1, 2), *w).flip(1, 2)
+        return torch_ref.scan_from_weights(x, *w)
+
+    m, u = refmodel.import_reference_models()
+    m.wavefront_scan_cuda = naive
+    torch.manual_seed(0)
+    backbone = m.Mamba2DBackbone(n_blocks=[2, 1, 1, 1], embed_dim=[16, 16, 32, 32], drop_path_rate=0.0,
+                                 res_scale_init_values=[1.0] * 4, inter_flip=True,
+                                 token_mixer=["2D_local", "2D_local", "RopeAttention", "RopeAttention"])
+    model = refmodel.Classifier(backbone, u.MlpHead(dim=32, n_classes=10)).double()
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(4, 3, 32, 32, generator=g, dtype=torch.float64)
+    labels = torch.randint(0, 10, (4,), generator=g)
+    return model, x, labels
+
+
+@pytest.mark.skipif(__import__("mamba2d_b200.refmodel", fromlist=["x"]).reference_root() is None,
+                    reason="no copy of the reference's models/ package")
+def test_ddp_training_step_equals_single_rank_step():
+    """The training configuration's step (forward + backward + AdamW with the reference's parameter
+    groups) on two gloo ranks with micro-batches and gradient accumulation gives the same updated
+    weights as one rank on the whole batch: the weight-gradient all-reduce averages what it should."""
+    from mamba2d_b200 import refmodel
+    world, port = 2, 31000 + os.getpid() % 2000
+    ret = mp.Manager().dict()
+    mp.spawn(_ddp_worker, args=(world, port, ret), nprocs=world, join=True)
+    model, x, labels = _tiny_classifier()
+    opt = refmodel.make_optimizer(model, lr=1e-3)
+    groups = refmodel.param_groups(model)
+    assert groups[1]["weight_decay"] == 0.0 and any(getattr(p, "_no_weight_decay", False) for p in groups[1]["params"])
+    assert all(p.dim() >= 2 for p in groups[0]["params"])
+    loss = refmodel.train_step(model, opt, x, labels, micro_batch=4, autocast_dtype=None)
+    want = [p.detach().numpy() for p in model.parameters()]
+    assert abs(0.5 * (ret[0]["loss"] + ret[1]["loss"]) - float(loss)) < 1e-9      # each rank reports its share's mean
+    refmodel.purge_models_modules()      # the model module imported here has the naive scan patched in
+    for r in (0, 1):
+        for a, b in zip(ret[r]["params"], want):
+            np.testing.assert_allclose(a, b, rtol=1e-7, atol=1e-9)

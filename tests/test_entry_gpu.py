@@ -139,3 +139,34 @@ def test_entry_step_replays_from_a_cuda_graph():
     assert rel_err(y.detach().cpu().numpy(), y_ref.cpu().numpy()) < 1e-6
     for name, t, r in zip(("x",) + WNAMES, [x] + ws, g_ref):
         assert rel_err(t.grad.cpu().numpy(), r.cpu().numpy()) < 1e-5, name
+
+
+@pytest.mark.parametrize("recomp", ["partial", "full"])
+def test_entry_inside_an_inductor_graph(recomp, monkeypatch):
+    """The reference compiles its classifier's forward with the default code-generating backend
+    (models/mamba2d_classifier.py:62).  Same check as above with that backend and a little PyTorch
+    arithmetic around the op for the code generator to fuse; guards in particular against outputs
+    that share storage with saved tensors losing their gradient under the graph compiler."""
+    from mamba2d_b200 import wavefront_scan_cuda
+    monkeypatch.setenv("CXX", "/usr/bin/g++")      # the host compiler the code generator may call
+    monkeypatch.setenv("CC", "/usr/bin/gcc")
+    torch._dynamo.reset()
+    w = inputs.make_module_params(64, 16, seed=5)
+    gen = torch.Generator().manual_seed(10)
+    x0 = torch.randn(2, 8, 6, 64, generator=gen)
+    gy = torch.randn(2, 8, 6, 64, generator=gen).cuda()
+
+    def block(x, *ws):
+        return torch.nn.functional.gelu(wavefront_scan_cuda(torch.nn.functional.gelu(x), *ws, recomp)) * 2.0
+
+    def run(fn):
+        x = x0.cuda().requires_grad_(True)
+        ws = [w[k].clone().cuda().requires_grad_(True) for k in WNAMES]
+        y = fn(x, *ws)
+        return [y.detach()] + list(torch.autograd.grad(y, [x] + ws, gy))
+
+    eager = run(block)
+    compiled = run(torch.compile(block))
+    for name, a, b in zip(("y", "d_x") + tuple("d_" + k for k in WNAMES), compiled, eager):
+        assert float(b.abs().max()) > 0, name
+        assert rel_err(a.cpu().numpy(), b.cpu().numpy()) < 1e-4, name

@@ -60,22 +60,29 @@ def test_full_batch_properties_fp32(D, HW):
         assert float((lo[idx] + hi[idx] - g[idx]).abs().max() / g[idx].abs().max()) < 1e-4
 
 
-@pytest.mark.parametrize("D,HW", STAGES[:2])
-def test_full_batch_bf16_against_fp32(D, HW):
-    """bf16 I/O computes in fp32 internally: on bf16-representable inputs it must agree with the fp32
-    path to bf16 output rounding."""
+@pytest.mark.parametrize("D,HW", STAGES)
+def test_full_batch_bf16_against_oracle(D, HW):
+    """bf16 I/O at the benchmark's full batch, all four stage shapes: the first and the last two images
+    against the fp64 oracle run on the same bf16-rounded inputs (2e-2 of the output scale), and the
+    batch sums against the fp32 path on the same values."""
     from mamba2d_b200 import scan_bwd, scan_fwd
-    inp = inputs.make_inputs(128, HW, HW, D, 16, seed=1)
-    q = {k: v.to(torch.bfloat16) for k, v in inp.items()}
-    d16 = {k: v.cuda() for k, v in q.items()}
-    d32 = {k: v.float().cuda() for k, v in q.items()}
-    y16 = scan_fwd(*[d16[k] for k in ORDER]).float()
-    y32 = scan_fwd(*[d32[k] for k in ORDER])
-    assert float((y16 - y32).abs().max() / y32.abs().max()) < 1e-2
-    g16 = scan_bwd(*[d16[k] for k in ORDER], d16["gy"])
-    g32 = scan_bwd(*[d32[k] for k in ORDER], d32["gy"])
-    for name, u, v in zip(GRADS, g16, g32):
-        assert float((u.float() - v).abs().max() / v.abs().max()) < 2e-2, name
+    inp = inputs.make_inputs(128, HW, HW, D, 16, seed=1, strided_bc=True)
+    d16 = _dev(inp, torch.bfloat16)
+    a = [d16[k] for k in ORDER]
+    y = scan_fwd(*a)
+    g = scan_bwd(*a, d16["gy"])
+    rounded = {k: v.to(torch.bfloat16).float() for k, v in inp.items()}
+    for sl in (slice(0, 2), slice(126, 128)):
+        sub_in = {k: (v[sl].contiguous() if v.dim() == 4 else v) for k, v in rounded.items()}
+        y_ref = cpu.forward(sub_in, "f64")
+        g_ref = cpu.backward(sub_in, mode="f64")
+        assert rel_err(y[sl].float().cpu().numpy(), y_ref) < 2e-2
+        for name, idx in (("d_x", 0), ("d_dT", 1), ("d_dL", 2), ("d_BT", 5), ("d_BL", 6), ("d_C", 7)):
+            assert rel_err(g[idx][sl].float().cpu().numpy(), g_ref[name]) < 2e-2, name
+    d32 = {k: v.float() for k, v in d16.items()}
+    g32 = scan_bwd(*[d32[k].contiguous() for k in ORDER], d32["gy"])
+    for idx in (3, 4, 8):      # d_AT, d_AL, d_D: sums over all 128 images
+        assert float((g[idx].float() - g32[idx]).abs().max() / g32[idx].abs().max()) < 2e-2
 
 
 def test_custom_ops_pass_opcheck():

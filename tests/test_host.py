@@ -124,3 +124,30 @@ def test_proj_params_gradients_survive_graph_capture():
     got = run(torch.compile(loss, backend="eager"))
     for name, a, b in zip(("x",) + names, got, want):
         assert float(b.abs().max()) > 0 and torch.allclose(a, b, rtol=1e-6, atol=0), name
+
+
+def test_status_word_check_raises(monkeypatch):
+    """The wrapper's reading of the status word, with a fake library and a host tensor standing in
+    for the workspace: nonzero raises, zero passes, M2D_CHECK_STATUS=0 never looks."""
+    import types
+    import torch
+    from mamba2d_b200 import wavefront_cuda as wc
+
+    fake = types.SimpleNamespace(m2d_scan_fwd_chain=lambda d: 4, m2d_scan_fwd_status_offset=lambda d: 0,
+                                 m2d_scan_bwd_chain=lambda d: 1, m2d_scan_bwd_status_offset=lambda d: 0)
+    monkeypatch.setattr(wc._lib, "lib", lambda: fake)
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
+    d = wc._lib.ScanDesc()
+    bad = torch.zeros(256, dtype=torch.uint8)
+    bad[0] = 1
+    good = torch.zeros(256, dtype=torch.uint8)
+    monkeypatch.setattr(wc, "_CHECK_STATUS", "auto")
+    with pytest.raises(RuntimeError, match="timed out"):
+        wc._check_status("fwd", d, bad)
+    wc._check_status("fwd", d, good)
+    wc._check_status("bwd", d, bad)              # one CTA per image: not looked at by default
+    monkeypatch.setattr(wc, "_CHECK_STATUS", "1")
+    with pytest.raises(RuntimeError, match="gradients are invalid"):
+        wc._check_status("bwd", d, bad)
+    monkeypatch.setattr(wc, "_CHECK_STATUS", "0")
+    wc._check_status("fwd", d, bad)

@@ -41,8 +41,8 @@ def test_noalloc_forward_equals_regular_forward_twice(kind, tol):
         inp = inputs.make_inputs(*shape, seed=seed)
         dev = {k: v.to("cuda", kind) for k, v in inp.items()}
         want = wc.scan_fwd(*[dev[k] for k in ORDER])
-        need = _lib.lib().m2d_scan_fwd_workspace(ctypes.byref(wc._make_desc(*[dev[k] for k in ORDER])[0]))
-        assert 0 < need <= _lib.NOALLOC_SCRATCH_BYTES
+        need = _lib.lib().m2d_scan_fwd_noalloc_need(ctypes.byref(wc._make_desc(*[dev[k] for k in ORDER])[0]))
+        assert 256 < need <= _lib.NOALLOC_SCRATCH_BYTES      # more than the status word: the ring is in use
         got = _call_noalloc(dev)
         torch.cuda.synchronize()
         scale = float(want.float().abs().max())
@@ -57,7 +57,7 @@ def test_noalloc_rejects_problems_beyond_its_capacity():
     d.dtype = _lib.M2D_F32
     d.B, d.H, d.W, d.E, d.N = 16, 64, 4096, 64, 16           # ring: 32 CTAs x 4096 columns x 2 KiB = 256 MiB
     d.BT_pitch = d.BL_pitch = d.C_pitch = 16
-    assert L.m2d_scan_fwd_workspace(ctypes.byref(d)) > _lib.NOALLOC_SCRATCH_BYTES
+    assert L.m2d_scan_fwd_noalloc_need(ctypes.byref(d)) > _lib.NOALLOC_SCRATCH_BYTES
     fake = ctypes.c_void_p(256)                               # never dereferenced: the size check comes first
     for name in ("x", "dT", "dL", "AT", "AL", "BT", "BL", "C", "D", "y"):
         setattr(d, name, fake)
