@@ -429,6 +429,7 @@ def m2dt_images_per_s(dev, world, batch=128, iters=5, variants=None):
     channels last, inference mode under bf16 autocast (the shipped precision is bf16-mixed).
     Variants: "ours" = the reference model calling this package's op, nothing else changed;
     "ours_native_corner" = the same with bottom-right blocks scanned in place instead of flipped;
+    "ours_native_corner_fused_act" = that plus the GELU after the scan folded into the scan's store;
     "reference" = the reference model calling its own kernels (its own Python module, prebuilt
     extension).  All ranks run the same replica; the reported figure sums the ranks."""
     import torch
@@ -442,14 +443,14 @@ def m2dt_images_per_s(dev, world, batch=128, iters=5, variants=None):
         x = torch.randn(batch, 3, 224, 224, generator=g).to(dev).contiguous(memory_format=torch.channels_last)
         out, state = {"batch_per_gpu": batch, "dtype": "bf16 autocast", "n_gpus": world}, None
         logits = {}
-        for v in variants or ("ours", "ours_native_corner", "reference"):
+        for v in variants or ("ours", "ours_native_corner", "ours_native_corner_fused_act", "reference"):
             try:
                 if v == "reference":
                     import importlib
                     load_reference_module()                      # models.kernels.wavefront_cuda = the reference's
                     mods = (importlib.import_module("models.mamba2d"), importlib.import_module("models.utils"))
                 else:
-                    mods = refmodel.import_reference_models(root, native_corner=(v == "ours_native_corner"))
+                    mods = refmodel.import_reference_models(root, native_corner=(v != "ours"), fuse_act2=v.endswith("fused_act"))
                 torch.manual_seed(0)
                 model = refmodel.build_classifier("M2D-T", mods).to(dev).eval()
                 if state is None:

@@ -71,6 +71,15 @@ typedef enum m2d_status {
 #define M2D_SCAN_REVERSE 1u
 
 /*
+ * M2D_SCAN_GELU_OUT (m2d_scan_fwd and m2d_scan_fwd_noalloc only; the backward rejects it): store
+ * gelu(y) instead of y, GELU in its erf form.  The reference block applies nn.GELU() to the scan's
+ * output as a separate elementwise pass (act2, models/mamba2d.py:169); at inference that pass can be
+ * folded into the scan's store.  For training the pre-activation y is needed by GELU's backward, so
+ * callers that need gradients leave the flag off and apply the activation themselves.
+ */
+#define M2D_SCAN_GELU_OUT 2u
+
+/*
  * M2D_SCAN_TEST_WITHHOLD: test hook, rejected with M2D_ERR_FLAGS unless the environment variable
  * M2D_TEST_HOOKS is 1.  In a launch that runs several CTAs per image, the CTA that owns the first
  * band of image 0 never publishes that band's column counter and every wait gives up after a few

@@ -16,6 +16,7 @@ inline void fill_common_args(ScanArgs& a, const m2d_scan_desc* d, const Plan& pl
     a.pBT = d->BT_pitch; a.pBL = d->BL_pitch; a.pC = d->C_pitch;
     a.Rb = pl.Rb; a.nbands = pl.nbands;
     a.chain = pl.chain;
+    a.act = (d->flags & M2D_SCAN_GELU_OUT) ? 1 : 0;
     const bool hook = (d->flags & M2D_SCAN_TEST_WITHHOLD) != 0;
     a.withhold = hook ? 1 : 0;
     a.wait_limit = hook ? (1 << 9) : kWaitPolls;

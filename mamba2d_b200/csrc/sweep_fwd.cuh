@@ -45,6 +45,7 @@ struct ScanArgs {
     int* status;              // nonzero if a wait on `progress` gave up (results are then invalid); never null
     int wait_limit;           // polls before such a wait gives up
     int withhold;             // test hook: the first band of image 0 never publishes its column counter
+    int act;                  // forward only: 1 = apply GELU (erf form) to y before it is stored
     // ---- backward only ----
     const void* gy;
     float4* hs;               // full state record: [b][group][H*W] blocks; a block is [4][32] float4 (fp32 I/O)
@@ -385,7 +386,11 @@ __device__ __forceinline__ void forward_sweep(const ScanArgs& a, float4* handoff
                         st.phs += HsBlock<io_t>::f4;
                     } else {
                         const float ysum = reduce_states(yacc[0], yacc[1], yacc[2], yacc[3], nq);
-                        if (y_lane) store1(static_cast<io_t*>(a.y), st.pixc * E + g * kGroup + lane, fmaf(sel4(cur.x, nq), D_own, ysum));
+                        float yv = fmaf(sel4(cur.x, nq), D_own, ysum);
+                        // optional output activation (the block applies GELU right after the scan:
+                        // models/mamba2d.py:167-169); one value per lane, so it costs one erf per lane and cell
+                        if (a.act) yv = 0.5f * yv * (1.f + erff(yv * 0.70710678118654752f));
+                        if (y_lane) store1(static_cast<io_t*>(a.y), st.pixc * E + g * kGroup + lane, yv);
                     }
                     st.pixc += a.dir;
             };

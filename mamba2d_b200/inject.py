@@ -91,7 +91,7 @@ def install_droppath_shim():
     return True
 
 
-def native_scan_corner(block_cls):
+def native_scan_corner(block_cls, fuse_act2=False):
     """Optional: make the reference's ``M2DBlock`` scan from its start corner in place.
 
     The reference block obtains ``scan_start == "BR"`` by flipping the activation on the way in and
@@ -104,6 +104,11 @@ def native_scan_corner(block_cls):
     input and its result is averaged in as it comes, without being flipped back
     (models/mamba2d.py:190-200).
 
+    With ``fuse_act2`` the GELU the block applies to the scan's output (``act2``,
+    models/mamba2d.py:169) is requested from the scan itself (``act_out="gelu"``), which folds it
+    into the kernel's store whenever no gradient is needed; ``double_scans`` blocks keep the separate
+    activation, because it acts on the average of two scans.
+
     Returns the class.  Call it after ``install()`` and after importing the model module:
 
         from models.mamba2d import M2DBlock
@@ -111,10 +116,11 @@ def native_scan_corner(block_cls):
     """
     scan = wavefront_cuda.wavefront_scan_cuda
 
-    def ssm(self, x):
+    def ssm(self, x, act_out=None):
         corner = getattr(self, "scan_start", "TL")
+        extra = {} if act_out is None else {"act_out": act_out}
         y = scan(x, self.AT_log, self.AL_log, self.x_proj.weight, self.dt_projT.weight, self.dt_projT.bias,
-                 self.dt_projL.weight, self.dt_projL.bias, self.D, self.recomp, scan_start=corner)
+                 self.dt_projL.weight, self.dt_projL.bias, self.D, self.recomp, scan_start=corner, **extra)
         if self.double_scans:
             other = "TL" if corner == "BR" else "BR"
             y_b = scan(x, self.AT_log_b, self.AL_log_b, self.x_proj_b.weight, self.dt_projT_b.weight,
@@ -125,7 +131,12 @@ def native_scan_corner(block_cls):
 
     def forward(self, x):
         local = self.local_path(self.local_norm(x)) if self.local_path else None
-        x = self.out_proj(self.act2(self.ssm(self.act1(self.in_proj(x)))))
+        gelu2 = fuse_act2 and not self.double_scans and type(self.act2).__name__ == "GELU" \
+            and getattr(self.act2, "approximate", "none") == "none"
+        if gelu2:
+            x = self.out_proj(self.ssm(self.act1(self.in_proj(x)), act_out="gelu"))
+        else:
+            x = self.out_proj(self.act2(self.ssm(self.act1(self.in_proj(x)))))
         return x if local is None else x + local
 
     block_cls.ssm = ssm

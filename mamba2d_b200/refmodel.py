@@ -49,11 +49,12 @@ def purge_models_modules():
         del sys.modules[k]
 
 
-def import_reference_models(root=None, native_corner=False):
+def import_reference_models(root=None, native_corner=False, fuse_act2=False):
     """``(models.mamba2d, models.utils)`` of the reference with this package's scan injected.
 
     With ``native_corner`` the block class scans bottom-right blocks in place instead of flipping
-    the activation around them (``inject.native_scan_corner``)."""
+    the activation around them (``inject.native_scan_corner``); ``fuse_act2`` also folds the GELU
+    after the scan into the scan's store where no gradient is needed."""
     root = root or reference_root()
     if root is None:
         raise RuntimeError("no reference checkout found: set M2D_REFERENCE_ROOT or run __graft_entry__.build() "
@@ -63,8 +64,8 @@ def import_reference_models(root=None, native_corner=False):
     inject.install(root)
     m = importlib.import_module("models.mamba2d")
     u = importlib.import_module("models.utils")
-    if native_corner:
-        inject.native_scan_corner(m.M2DBlock)
+    if native_corner or fuse_act2:
+        inject.native_scan_corner(m.M2DBlock, fuse_act2=fuse_act2)
     return m, u
 
 

@@ -98,7 +98,7 @@ def _check_inputs(x, dT, dL, AT, AL, BT, BL, C, D, gy=None):
     return B, H, W, E, N
 
 
-def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D, reverse=False):
+def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D, reverse=False, gelu_out=False):
     B, H, W, E = x.shape
     N = AT.shape[1]
     keep = []   # tensors that must outlive the launch call
@@ -106,7 +106,7 @@ def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D, reverse=False):
     d.struct_bytes = ctypes.sizeof(_lib.ScanDesc)
     d.dtype = _DTYPES[x.dtype]
     d.B, d.H, d.W, d.E, d.N = B, H, W, E, N
-    d.flags = _lib.M2D_SCAN_REVERSE if reverse else 0
+    d.flags = (_lib.M2D_SCAN_REVERSE if reverse else 0) | (_lib.M2D_SCAN_GELU_OUT if gelu_out else 0)
     for name, t in (("x", x), ("dT", dT), ("dL", dL), ("AT", AT), ("AL", AL), ("D", D)):
         t = t.contiguous()
         keep.append(t)
@@ -127,8 +127,12 @@ def _workspace(d, nbytes, device, keep):
         d.workspace_bytes = int(nbytes)
 
 
-def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
+def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False, gelu_out=False):
     """Fused forward: y (B,H,W,E) in ``x.dtype``.  Inputs as ``wf_cuda_fn_pr.apply`` takes them.
+
+    ``gelu_out=True`` returns ``gelu(y)`` (erf form), applied inside the kernel's store: what the
+    reference block computes with a separate ``nn.GELU()`` pass after the scan (models/mamba2d.py:169).
+    There is no backward for it; it is for inference.
 
     ``reverse=True`` scans from the bottom-right corner: the result equals
     ``scan_fwd(*[t.flip(1, 2) for t in pixel_tensors], ...).flip(1, 2)`` without any copy.
@@ -140,7 +144,7 @@ def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
     _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
     L = _lib.lib()
     with torch.cuda.device(x.device):
-        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, gelu_out)
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         d.y = y.data_ptr()
         _workspace(d, L.m2d_scan_fwd_workspace(ctypes.byref(d)), x.device, keep)
@@ -502,7 +506,7 @@ class wf_cuda_fn_fr(torch.autograd.Function):
 
 
 def wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, recomp="partial",
-                        scan_start="TL"):
+                        scan_start="TL", act_out=None):
     """The op as ``M2DBlock.ssm`` calls it.
 
     Args:
@@ -510,12 +514,17 @@ def wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_
             weights and recomputes the projections in backward (less memory, slower).
         scan_start: ``"TL"`` (the reference's only direction) or ``"BR"``: scan from the bottom-right
             corner, equal to ``wavefront_scan_cuda(x.flip(1, 2), ...).flip(1, 2)`` without the copies.
+        act_out: ``None`` or ``"gelu"``: return ``gelu(y)``, erf form, as the block's ``act2`` computes
+            it (models/mamba2d.py:169).  Without gradients in play the activation is applied inside
+            the kernel's store; otherwise it is an ordinary PyTorch op after the scan.
     Raises:
         ValueError: if H < 2 or W < 2, or for an unknown ``recomp`` (same conditions as the
             reference) or ``scan_start``.
     """
     if scan_start not in ("TL", "BR"):
         raise ValueError(f"Unknown scan start corner, got {scan_start}...")
+    if act_out not in (None, "gelu"):
+        raise ValueError(f"Unknown output activation, got {act_out}...")
     reverse = scan_start == "BR"
     _, H, W, _ = x.shape
     if H < 2 or W < 2:
@@ -528,10 +537,18 @@ def wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_
     dt_projL_b = dt_projL_b.to(x.dtype)
     D = D.to(x.dtype)
 
+    if recomp not in ("partial", "full"):
+        raise ValueError(f"Unknown recomputation mode, got {recomp}...")
+    params = (x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D)
+    if act_out == "gelu" and not (torch.is_grad_enabled() and any(t.requires_grad for t in params)) \
+            and not torch.compiler.is_compiling():
+        # nothing to differentiate: one kernel for scan + activation
+        (deltaT, deltaL, AT, AL, BT, BL, C), _ = _proj_forward(*params[:-1])
+        return scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, gelu_out=True)
     if recomp == "partial":
         deltaT, deltaL, AT, AL, BT, BL, C = proj_params(
             x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
-        return wf_cuda_fn_pr.apply(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
-    if recomp == "full":
-        return wf_cuda_fn_fr.apply(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, reverse)
-    raise ValueError(f"Unknown recomputation mode, got {recomp}...")
+        y = wf_cuda_fn_pr.apply(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+    else:
+        y = wf_cuda_fn_fr.apply(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, reverse)
+    return F.gelu(y) if act_out == "gelu" else y

@@ -170,3 +170,29 @@ def test_entry_inside_an_inductor_graph(recomp, monkeypatch):
     for name, a, b in zip(("y", "d_x") + tuple("d_" + k for k in WNAMES), compiled, eager):
         assert float(b.abs().max()) > 0, name
         assert rel_err(a.cpu().numpy(), b.cpu().numpy()) < 1e-4, name
+
+
+def test_entry_output_activation_with_and_without_gradients():
+    """act_out="gelu": folded into the kernel where nothing is differentiated, an ordinary op under
+    autograd; both equal gelu(entry)."""
+    from mamba2d_b200 import wavefront_scan_cuda
+    w = inputs.make_module_params(64, 16, seed=7)
+    gen = torch.Generator().manual_seed(13)
+    x = torch.randn(2, 11, 8, 64, generator=gen).cuda()
+    gy = torch.randn(2, 11, 8, 64, generator=gen).cuda()
+    ws = [w[k].clone().cuda() for k in WNAMES]
+    with torch.no_grad():
+        plain = torch.nn.functional.gelu(wavefront_scan_cuda(x, *ws))
+        fused = wavefront_scan_cuda(x, *ws, act_out="gelu")
+        fused_br = wavefront_scan_cuda(x, *ws, "full", scan_start="BR", act_out="gelu")
+        plain_br = torch.nn.functional.gelu(wavefront_scan_cuda(x, *ws, "full", scan_start="BR"))
+    assert rel_err(fused.cpu().numpy(), plain.cpu().numpy()) < 1e-5
+    assert rel_err(fused_br.cpu().numpy(), plain_br.cpu().numpy()) < 1e-5
+    xg = x.clone().requires_grad_(True)
+    wg = [t.clone().requires_grad_(True) for t in ws]
+    a = torch.autograd.grad(wavefront_scan_cuda(xg, *wg, act_out="gelu"), [xg] + wg, gy)
+    b = torch.autograd.grad(torch.nn.functional.gelu(wavefront_scan_cuda(xg, *wg)), [xg] + wg, gy)
+    for u, v in zip(a, b):
+        assert rel_err(u.cpu().numpy(), v.cpu().numpy()) < 1e-5
+    with pytest.raises(ValueError):
+        wavefront_scan_cuda(x, *ws, act_out="relu")

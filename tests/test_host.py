@@ -10,12 +10,12 @@ from oracle import inputs, torch_ref
 
 def test_public_signature_matches_reference_entry():
     """Argument names and order of the reference's wavefront_scan_cuda
-    (models/kernels/wavefront_cuda.py:315 in the reference); the one addition, the start corner,
-    comes last and defaults to the reference's direction."""
+    (models/kernels/wavefront_cuda.py:315 in the reference); the two additions, the start corner and
+    the output activation, come last and default to the reference's behaviour."""
     sig = inspect.signature(wc.wavefront_scan_cuda).parameters
     assert list(sig) == ["x", "AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w",
-                         "dt_projL_b", "D", "recomp", "scan_start"]
-    assert sig["recomp"].default == "partial" and sig["scan_start"].default == "TL"
+                         "dt_projL_b", "D", "recomp", "scan_start", "act_out"]
+    assert sig["recomp"].default == "partial" and sig["scan_start"].default == "TL" and sig["act_out"].default is None
     pr = inspect.signature(wc.wf_cuda_fn_pr.forward).parameters
     assert list(pr)[1:] == ["x", "deltaT", "deltaL", "AT", "AL", "BT", "BL", "C", "D", "reverse"]
     assert pr["reverse"].default is False

@@ -33,7 +33,8 @@ def test_reference_block_imports_replacement():
 @pytest.mark.skipif(not os.path.exists(os.path.join(REF, "models", "mamba2d.py")), reason="reference checkout not present")
 @pytest.mark.parametrize("corner", ["TL", "BR"])
 @pytest.mark.parametrize("local_path", [False, True])
-def test_block_without_flips_equals_reference_block(corner, local_path, monkeypatch):
+@pytest.mark.parametrize("fuse_act2", [False, True])
+def test_block_without_flips_equals_reference_block(corner, local_path, fuse_act2, monkeypatch):
     """native_scan_corner() removes the flip copies of a bottom-right block.  Checked on the CPU
     with a naive PyTorch scan standing in for the kernels (forward direction by definition,
     bottom-right by flipping around it): the reference's own forward() and the patched one must
@@ -44,12 +45,11 @@ def test_block_without_flips_equals_reference_block(corner, local_path, monkeypa
     from mamba2d_b200 import wavefront_cuda
     from oracle import torch_ref
 
-    def naive(x, *w, recomp="partial", scan_start="TL"):
+    def naive(x, *w, recomp="partial", scan_start="TL", act_out=None):
         if len(w) == 9:
             *w, recomp = w
-        if scan_start == "BR":
-            return torch_ref.scan_from_weights(x.flip(1, 2), *w).flip(1, 2)
-        return torch_ref.scan_from_weights(x, *w)
+        y = torch_ref.scan_from_weights(x.flip(1, 2), *w).flip(1, 2) if scan_start == "BR" else torch_ref.scan_from_weights(x, *w)
+        return torch.nn.functional.gelu(y) if act_out == "gelu" else y
 
     inject.install_droppath_shim()
     inject.install(REF)
@@ -63,7 +63,7 @@ def test_block_without_flips_equals_reference_block(corner, local_path, monkeypa
 
         class Patched(m.M2DBlock):
             pass
-        inject.native_scan_corner(Patched)
+        inject.native_scan_corner(Patched, fuse_act2=fuse_act2)
         new_blk = Patched(d_model=16, scan_start=corner, local_path=local_path).double()
         new_blk.load_state_dict(ref_blk.state_dict())
         x = torch.randn(2, 5, 4, 16, dtype=torch.float64)

@@ -62,12 +62,12 @@ def test_classifier_logits_match_the_reference_kernels():
     g = torch.Generator().manual_seed(3)
     x = torch.randn(2, 3, 224, 224, generator=g).cuda().contiguous(memory_format=torch.channels_last)
     logits, state = {}, None
-    for v in ("ours", "ours_native_corner", "reference"):
+    for v in ("ours", "ours_native_corner", "ours_native_corner_fused_act", "reference"):
         if v == "reference":
             bench.load_reference_module()
             mods = (importlib.import_module("models.mamba2d"), importlib.import_module("models.utils"))
         else:
-            mods = refmodel.import_reference_models(native_corner=(v == "ours_native_corner"))
+            mods = refmodel.import_reference_models(native_corner=(v != "ours"), fuse_act2=v.endswith("fused_act"))
         torch.manual_seed(0)
         model = refmodel.build_classifier("M2D-T", mods).cuda().eval()
         if state is None:
@@ -80,3 +80,36 @@ def test_classifier_logits_match_the_reference_kernels():
     refmodel.purge_models_modules()
     assert rel_err(logits["ours"], logits["reference"]) < 1e-3
     assert rel_err(logits["ours_native_corner"], logits["reference"]) < 1e-3
+    assert rel_err(logits["ours_native_corner_fused_act"], logits["reference"]) < 1e-3
+
+
+def test_block_under_autocast_takes_the_fused_projection_kernels(monkeypatch):
+    """The shipped precision is bf16-mixed: inside the block the activation reaching the scan is bf16
+    and the entry casts the projection weights to it, so the fused projection kernels (not the
+    PyTorch formulation) must run, forward and backward, and the result must agree with the fp32 run."""
+    from mamba2d_b200 import wavefront_cuda as wc
+    m, _ = refmodel.import_reference_models()
+    torch.manual_seed(0)
+    blk = m.M2DBlock(d_model=64, local_path=True).cuda()
+    g = torch.Generator().manual_seed(2)
+    x, gy = torch.randn(4, 14, 14, 64, generator=g).cuda(), torch.randn(4, 14, 14, 64, generator=g).cuda()
+    calls = {"fwd": 0, "bwd": 0}
+    f0, b0 = wc._dtproj_fwd, wc._dtproj_bwd
+    monkeypatch.setitem(wc._EAGER, wc.dtproj_fwd_op, lambda *a: (calls.__setitem__("fwd", calls["fwd"] + 1), f0(*a))[1])
+    monkeypatch.setitem(wc._EAGER, wc.dtproj_bwd_op, lambda *a: (calls.__setitem__("bwd", calls["bwd"] + 1), b0(*a))[1])
+
+    def run(autocast):
+        xi = x.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+            y = blk(xi)
+        grads = torch.autograd.grad(y.float(), [xi] + list(blk.parameters()), gy)
+        return [y.detach().float()] + [t.float() for t in grads]
+
+    ref = run(False)
+    n_fp32 = dict(calls)
+    got = run(True)
+    assert n_fp32 == {"fwd": 1, "bwd": 1} and calls == {"fwd": 2, "bwd": 2}
+    for k, (a, b) in enumerate(zip(got, ref)):
+        # y and d_x at the bf16 bar; parameter gradients are long bf16 sums (some of them scalars)
+        assert rel_err(a.cpu().numpy(), b.cpu().numpy()) < (3e-2 if k < 2 else 1e-1)
+    refmodel.purge_models_modules()

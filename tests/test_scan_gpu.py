@@ -144,3 +144,24 @@ def test_backward_twice_same_workspace_sizes():
     b = run_bwd(inp, "f32")
     for k in GRADS:
         assert rel_err(a[k], b[k]) < 1e-5, k
+
+
+@pytest.mark.parametrize("kind", ["f32", "bf16"])
+@pytest.mark.parametrize("reverse", [False, True])
+def test_forward_with_output_gelu(kind, reverse):
+    """The GELU the block applies after the scan, folded into the kernel's store, against the oracle's
+    y passed through the erf-form GELU in fp64."""
+    from mamba2d_b200 import scan_fwd
+    from scipy.special import erf
+    inp = inputs.make_inputs(3, 20, 9, 96, 16, seed=31)
+    ref_in = bf16_round_inputs(inp) if kind == "bf16" else inp
+    if reverse:
+        flipped = {k: (v.flip(1, 2).contiguous() if v.dim() == 4 else v) for k, v in ref_in.items()}
+        y_ref = np.flip(cpu.forward(flipped, "f64"), (1, 2))
+    else:
+        y_ref = cpu.forward(ref_in, "f64")
+    want = 0.5 * y_ref * (1.0 + erf(y_ref / np.sqrt(2.0)))
+    d = to_dev(inp, TDT[kind])
+    got = scan_fwd(*[d[k] for k in ORDER], reverse=reverse, gelu_out=True)
+    torch.cuda.synchronize()
+    assert rel_err(got.float().cpu().numpy(), want) < TOL[kind]
