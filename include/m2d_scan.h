@@ -80,6 +80,16 @@ typedef enum m2d_status {
 #define M2D_SCAN_GELU_OUT 2u
 
 /*
+ * M2D_SCAN_A_LOG: desc->AT and desc->AL point to the FP32 parameters AT_log, AL_log (E,N), whatever
+ * `dtype` is, and the kernels use A = -exp(A_log), rounded to `dtype` as the reference's cast does
+ * (models/kernels/wavefront_cuda.py:72-73, :89-90).  In the backward desc->d_AT and desc->d_AL then
+ * receive the gradient with respect to A_log (= d_A * A) as FP32 (E,N) arrays.  This folds the
+ * reference's `-torch.exp(A_log.float())`, its casts and their backward -- a handful of tiny
+ * elementwise launches per call -- into the kernels.
+ */
+#define M2D_SCAN_A_LOG 4u
+
+/*
  * M2D_SCAN_TEST_WITHHOLD: test hook, rejected with M2D_ERR_FLAGS unless the environment variable
  * M2D_TEST_HOOKS is 1.  In a launch that runs several CTAs per image, the CTA that owns the first
  * band of image 0 never publishes that band's column counter and every wait gives up after a few
@@ -92,7 +102,8 @@ typedef enum m2d_status {
 /*
  * Problem descriptor.  Tensor layouts are the ones the reference op receives:
  *   x, dT, dL, y, gy, d_x, d_dT, d_dL   (B,H,W,E) contiguous, channels last
- *   AT, AL, d_AT, d_AL                  (E,N) contiguous; A = -exp(A_log) already applied
+ *   AT, AL, d_AT, d_AL                  (E,N) contiguous; A = -exp(A_log) already applied (but see
+ *                                       M2D_SCAN_A_LOG)
  *   D, d_D                              (E)
  *   BT, BL, C                           (B,H,W,N) with unit stride over N and a per-tensor pixel
  *                                       pitch in ELEMENTS (row stride W*pitch, batch stride

@@ -12,6 +12,7 @@ LIB_PATH = os.environ.get("M2D_SCAN_LIB", os.path.join(HERE, "libm2d_scan.so")) 
 M2D_F32, M2D_BF16 = 0, 1
 M2D_SCAN_REVERSE = 1
 M2D_SCAN_GELU_OUT = 2
+M2D_SCAN_A_LOG = 4
 M2D_SCAN_TEST_WITHHOLD = 0x100
 ABI_VERSION = 3
 NOALLOC_SCRATCH_BYTES = 32 << 20     # M2D_NOALLOC_SCRATCH_BYTES in include/m2d_scan.h

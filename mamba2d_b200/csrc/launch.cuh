@@ -17,6 +17,7 @@ inline void fill_common_args(ScanArgs& a, const m2d_scan_desc* d, const Plan& pl
     a.Rb = pl.Rb; a.nbands = pl.nbands;
     a.chain = pl.chain;
     a.act = (d->flags & M2D_SCAN_GELU_OUT) ? 1 : 0;
+    a.a_log = (d->flags & M2D_SCAN_A_LOG) ? 1 : 0;
     const bool hook = (d->flags & M2D_SCAN_TEST_WITHHOLD) != 0;
     a.withhold = hook ? 1 : 0;
     a.wait_limit = hook ? (1 << 9) : kWaitPolls;

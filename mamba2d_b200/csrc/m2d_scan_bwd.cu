@@ -5,6 +5,12 @@
 #include "launch.cuh"
 #include "sweep_bwd.cuh"
 
+// Row-warps per CTA of the backward kernel (two CTAs per SM): the register budget per thread follows
+// from it (6 warps: 168 registers).
+#ifndef M2D_BWD_MAXW
+#define M2D_BWD_MAXW 6
+#endif
+
 namespace m2d {
 
 // Workspace layout of the backward pass (all regions 256-byte aligned):
@@ -48,14 +54,14 @@ inline BwdLayout bwd_layout(const m2d_scan_desc* d, const Plan& p) {
 }
 
 inline Plan plan_bwd(const m2d_scan_desc* d) {
-    // tuning knob: M2D_BWD_WARPS=<1..6> overrides the row-warps per CTA of the backward kernel
-    int maxw = 6;
-    if (const char* e = getenv("M2D_BWD_WARPS")) { const int v = atoi(e); if (v >= 1 && v <= 6) maxw = v; }
-    Plan p = plan_best(d, maxw, 12);
+    // tuning knob: M2D_BWD_WARPS=<1..max> overrides the row-warps per CTA of the backward kernel
+    int maxw = M2D_BWD_MAXW;
+    if (const char* e = getenv("M2D_BWD_WARPS")) { const int v = atoi(e); if (v >= 1 && v <= M2D_BWD_MAXW) maxw = v; }
+    Plan p = plan_best(d, maxw, 2 * M2D_BWD_MAXW);
     p.smem = bwd_smem_bytes(p.warps) + kParamF4 * sizeof(float4);
     // few images on a large map: chain CTAs along the bands of an image, as the forward does
     {
-        const long long slots = (long long)(12 / p.warps > 0 ? 12 / p.warps : 1) * sm_count();
+        const long long slots = (long long)(2 * M2D_BWD_MAXW / p.warps > 0 ? 2 * M2D_BWD_MAXW / p.warps : 1) * sm_count();
         const long long ctas = (long long)p.grid_x * p.groups;
         if (p.nbands > 1 && ctas * 2 <= slots) p.chain = bound_chain(slots / ctas, p.nbands, d->W, p.Rb);
     }
@@ -64,7 +70,7 @@ inline Plan plan_bwd(const m2d_scan_desc* d) {
 }
 
 template <typename io_t, bool VEC, bool CHAINED>
-__global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
+__global__ void __launch_bounds__(M2D_BWD_MAXW * 32, 2) m2d_bwd_kernel(const ScanArgs a) {
     extern __shared__ float4 handoff[];
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
@@ -88,7 +94,7 @@ __global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
     }
     __syncthreads();
     float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + bwd_smem_bytes(nwarps));
-    if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane);
+    if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane, a.a_log);
     __syncthreads();
 
     // gridDim.x = chains x a.chain: CTA (chain_id, cpos) walks images chain_id, chain_id + chains, ...
@@ -132,8 +138,14 @@ __global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
                     if (n < nv) {
-                        atomicAdd(a.accAT + (size_t)(ch0 + c) * a.N + n0 + n, dAT[c][n]);
-                        atomicAdd(a.accAL + (size_t)(ch0 + c) * a.N + n0 + n, dAL[c][n]);
+                        const long long idx = (long long)(ch0 + c) * a.N + n0 + n;
+                        // with A given as A_log the gradient asked for is d_A_log = d_A * A (A = -exp(A_log),
+                        // models/kernels/wavefront_cuda.py:72-73); the product is linear, so every CTA
+                        // scales its own partial sum
+                        const float sT = a.a_log ? load_A<io_t>(a.AT, idx, 1, true) : 1.f;
+                        const float sL = a.a_log ? load_A<io_t>(a.AL, idx, 1, true) : 1.f;
+                        atomicAdd(a.accAT + idx, dAT[c][n] * sT);
+                        atomicAdd(a.accAL + idx, dAL[c][n] * sL);
                     }
                 }
                 if (nq == 0) atomicAdd(a.accD + ch0 + c, dD[c]);
@@ -142,10 +154,11 @@ __global__ void __launch_bounds__(192, 2) m2d_bwd_kernel(const ScanArgs a) {
     }
 }
 
-// bf16 I/O: cast the fp32 accumulators into the caller's gradient tensors.
+// bf16 I/O: cast the fp32 accumulators into the caller's gradient tensors (d_AT / d_AL stay fp32 when
+// they are gradients of the fp32 parameter A_log).
 template <typename io_t>
-__global__ void m2d_bwd_finalize(const float* __restrict__ acc, io_t* d_BT, io_t* d_BL, io_t* d_C, io_t* d_AT, io_t* d_AL,
-                                 io_t* d_D, long long npn, long long en, int E) {
+__global__ void m2d_bwd_finalize(const float* __restrict__ acc, io_t* d_BT, io_t* d_BL, io_t* d_C, void* d_AT, void* d_AL,
+                                 io_t* d_D, long long npn, long long en, int E, int a_log) {
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long nthreads = (long long)gridDim.x * blockDim.x;
     for (long long k = tid; k < npn; k += nthreads) {
@@ -155,8 +168,13 @@ __global__ void m2d_bwd_finalize(const float* __restrict__ acc, io_t* d_BT, io_t
     }
     const float* accA = acc + 3 * npn;
     for (long long k = tid; k < en; k += nthreads) {
-        store1(d_AT, k, accA[k]);
-        store1(d_AL, k, accA[en + k]);
+        if (a_log) {
+            static_cast<float*>(d_AT)[k] = accA[k];
+            static_cast<float*>(d_AL)[k] = accA[en + k];
+        } else {
+            store1(static_cast<io_t*>(d_AT), k, accA[k]);
+            store1(static_cast<io_t*>(d_AL), k, accA[en + k]);
+        }
     }
     for (long long k = tid; k < E; k += nthreads) store1(d_D, k, accA[2 * en + k]);
 }
@@ -214,9 +232,8 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
     if (d->dtype != M2D_F32) {
         const int fin_blocks = (int)((npn + 255) / 256 < 148 * 8 ? (npn + 255) / 256 : 148 * 8);
         m2d_bwd_finalize<io_t><<<fin_blocks, 256, 0, st>>>(a.accBT, static_cast<io_t*>(d->d_BT), static_cast<io_t*>(d->d_BL),
-                                                          static_cast<io_t*>(d->d_C), static_cast<io_t*>(d->d_AT),
-                                                          static_cast<io_t*>(d->d_AL), static_cast<io_t*>(d->d_D),
-                                                          (long long)npn, (long long)en, d->E);
+                                                          static_cast<io_t*>(d->d_C), d->d_AT, d->d_AL, static_cast<io_t*>(d->d_D),
+                                                          (long long)npn, (long long)en, d->E, a.a_log);
         if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
     }
     return M2D_OK;

@@ -20,7 +20,7 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
     const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
     __syncthreads();
     float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes((blockDim.x >> 5), CB));
-    if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane);
+    if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane, a.a_log);
     __syncthreads();
 
     // gridDim.x = chains x a.chain: CTA (chain_id, cpos) walks images chain_id, chain_id + chains, ...

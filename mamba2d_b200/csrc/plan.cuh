@@ -27,7 +27,7 @@ inline int check_desc(const m2d_scan_desc* d, bool bwd, bool need_ptrs) {
     if (d->struct_bytes != sizeof(m2d_scan_desc)) return M2D_ERR_ABI;
     if (d->dtype != M2D_F32 && d->dtype != M2D_BF16) return M2D_ERR_DTYPE;
     {
-        unsigned known = M2D_SCAN_REVERSE;
+        unsigned known = M2D_SCAN_REVERSE | M2D_SCAN_A_LOG;
         if (!bwd) known |= M2D_SCAN_GELU_OUT;      // an output activation exists in the forward only
         if (test_hooks_enabled()) known |= M2D_SCAN_TEST_WITHHOLD;
         if (d->flags & ~known) return M2D_ERR_FLAGS;

@@ -46,6 +46,7 @@ struct ScanArgs {
     int wait_limit;           // polls before such a wait gives up
     int withhold;             // test hook: the first band of image 0 never publishes its column counter
     int act;                  // forward only: 1 = apply GELU (erf form) to y before it is stored
+    int a_log;                // AT / AL hold the fp32 parameter A_log (A = -exp(A_log)); d_AT / d_AL are then fp32 d_A_log
     // ---- backward only ----
     const void* gy;
     float4* hs;               // full state record: [b][group][H*W] blocks; a block is [4][32] float4 (fp32 I/O)
@@ -78,16 +79,29 @@ __host__ __device__ inline size_t sweep_smem_bytes(int warps, int cb = 1) { retu
 // The per-(channel,state) parameters A*log2(e) of the CTA's 32 channels live in shared memory
 // behind everything else: [AT | AL][4 channels][32 lanes] float4 (4 KiB), read block by block.
 constexpr int kParamF4 = 2 * 4 * 32;
+// Element (e, n) of AT / AL as a float.  With `a_log` the tensors hold the fp32 parameter A_log and
+// A = -exp(A_log), rounded to the I/O type the way the reference's cast does
+// (models/kernels/wavefront_cuda.py:72-73, :89-90); `exact` skips that rounding (used for the
+// gradient d_A_log = d_A * A, where the reference multiplies by the fp32 value).
 template <typename io_t>
-__device__ __forceinline__ void stage_params(float4* dst, const void* AT, const void* AL, int N, int ch0, int chv, int n0, int nv, int lane) {
+__device__ __forceinline__ float load_A(const void* A, long long idx, int a_log, bool exact = false) {
+    if (!a_log) return load1(static_cast<const io_t*>(A), idx);
+    const float v = -expf(__ldg(static_cast<const float*>(A) + idx));
+    if (sizeof(io_t) == 2 && !exact) return __bfloat162float(__float2bfloat16_rn(v));
+    return v;
+}
+
+template <typename io_t>
+__device__ __forceinline__ void stage_params(float4* dst, const void* AT, const void* AL, int N, int ch0, int chv, int n0, int nv, int lane,
+                                             int a_log) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         float t[4], l[4];
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
             const bool ok = (c < chv) && (n < nv);
-            t[n] = ok ? load1(static_cast<const io_t*>(AT), (long long)(ch0 + c) * N + n0 + n) * kLog2e : 0.f;
-            l[n] = ok ? load1(static_cast<const io_t*>(AL), (long long)(ch0 + c) * N + n0 + n) * kLog2e : 0.f;
+            t[n] = ok ? load_A<io_t>(AT, (long long)(ch0 + c) * N + n0 + n, a_log) * kLog2e : 0.f;
+            l[n] = ok ? load_A<io_t>(AL, (long long)(ch0 + c) * N + n0 + n, a_log) * kLog2e : 0.f;
         }
         dst[c * 32 + lane] = make_float4(t[0], t[1], t[2], t[3]);
         dst[128 + c * 32 + lane] = make_float4(l[0], l[1], l[2], l[3]);

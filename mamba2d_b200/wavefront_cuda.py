@@ -72,7 +72,7 @@ def _pixel_pitch(t, H, W, N):
     return t.contiguous(), N
 
 
-def _check_inputs(x, dT, dL, AT, AL, BT, BL, C, D, gy=None):
+def _check_inputs(x, dT, dL, AT, AL, BT, BL, C, D, gy=None, a_log=False):
     if x.dim() != 4:
         raise RuntimeError(f"x must be (B,H,W,E), got {tuple(x.shape)}")
     if not x.is_cuda:
@@ -91,14 +91,15 @@ def _check_inputs(x, dT, dL, AT, AL, BT, BL, C, D, gy=None):
         if tuple(t.shape) != shape:
             raise RuntimeError(f"{name} must have shape {shape}, got {tuple(t.shape)}")
     for name, t in [("x", x), ("AT", AT)] + [(k, v[0]) for k, v in want.items()]:
-        if t.dtype != x.dtype:
-            raise RuntimeError(f"{name} has dtype {t.dtype}, expected {x.dtype}")
+        expect = torch.float32 if (a_log and name in ("AT", "AL")) else x.dtype     # A_log is an fp32 parameter
+        if t.dtype != expect:
+            raise RuntimeError(f"{name} has dtype {t.dtype}, expected {expect}")
         if t.device != x.device:
             raise RuntimeError(f"{name} is on {t.device}, expected {x.device}")
     return B, H, W, E, N
 
 
-def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D, reverse=False, gelu_out=False):
+def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D, reverse=False, gelu_out=False, a_log=False):
     B, H, W, E = x.shape
     N = AT.shape[1]
     keep = []   # tensors that must outlive the launch call
@@ -106,7 +107,8 @@ def _make_desc(x, dT, dL, AT, AL, BT, BL, C, D, reverse=False, gelu_out=False):
     d.struct_bytes = ctypes.sizeof(_lib.ScanDesc)
     d.dtype = _DTYPES[x.dtype]
     d.B, d.H, d.W, d.E, d.N = B, H, W, E, N
-    d.flags = (_lib.M2D_SCAN_REVERSE if reverse else 0) | (_lib.M2D_SCAN_GELU_OUT if gelu_out else 0)
+    d.flags = ((_lib.M2D_SCAN_REVERSE if reverse else 0) | (_lib.M2D_SCAN_GELU_OUT if gelu_out else 0)
+               | (_lib.M2D_SCAN_A_LOG if a_log else 0))
     for name, t in (("x", x), ("dT", dT), ("dL", dL), ("AT", AT), ("AL", AL), ("D", D)):
         t = t.contiguous()
         keep.append(t)
@@ -127,12 +129,16 @@ def _workspace(d, nbytes, device, keep):
         d.workspace_bytes = int(nbytes)
 
 
-def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False, gelu_out=False):
+def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False, gelu_out=False, a_log=False):
     """Fused forward: y (B,H,W,E) in ``x.dtype``.  Inputs as ``wf_cuda_fn_pr.apply`` takes them.
 
     ``gelu_out=True`` returns ``gelu(y)`` (erf form), applied inside the kernel's store: what the
     reference block computes with a separate ``nn.GELU()`` pass after the scan (models/mamba2d.py:169).
     There is no backward for it; it is for inference.
+
+    ``a_log=True``: ``AT`` / ``AL`` are the fp32 parameters ``AT_log`` / ``AL_log`` and the kernel uses
+    ``A = -exp(A_log)`` (rounded to ``x.dtype`` as the reference's cast does,
+    models/kernels/wavefront_cuda.py:72-73, :89-90), which saves the elementwise launches that compute A.
 
     ``reverse=True`` scans from the bottom-right corner: the result equals
     ``scan_fwd(*[t.flip(1, 2) for t in pixel_tensors], ...).flip(1, 2)`` without any copy.
@@ -141,10 +147,10 @@ def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False, gelu_out=Fa
     with bounded polling.  After such a launch the wrapper synchronises and raises if a wait gave
     up (status word in the workspace, see m2d_scan_fwd_status_offset); ``M2D_CHECK_STATUS=1``
     extends that check to every launch, ``M2D_CHECK_STATUS=0`` switches it off."""
-    _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
+    _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D, a_log=a_log)
     L = _lib.lib()
     with torch.cuda.device(x.device):
-        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, gelu_out)
+        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, gelu_out, a_log)
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         d.y = y.data_ptr()
         _workspace(d, L.m2d_scan_fwd_workspace(ctypes.byref(d)), x.device, keep)
@@ -154,18 +160,21 @@ def scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False, gelu_out=Fa
     return y
 
 
-def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False, shared_storage=True):
+def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False, shared_storage=True, a_log=False):
     """Fused backward with recomputation.  Returns the nine gradients
     (d_x, d_deltaT, d_deltaL, d_AT, d_AL, d_BT, d_BL, d_C, d_D), all in ``x.dtype``.
 
     With ``shared_storage`` the reduced gradients are disjoint views of two allocations (per-pixel
     and per-channel ones), which lets the library zero them with two memsets; the registered
-    operator asks for separate tensors, because operator outputs must not share storage."""
-    B, H, W, E, N = _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output)
+    operator asks for separate tensors, because operator outputs must not share storage.
+
+    ``a_log=True``: ``AT`` / ``AL`` are the fp32 parameters A_log (see ``scan_fwd``) and ``d_AT`` / ``d_AL``
+    come back as fp32 gradients with respect to them (``d_A * A``)."""
+    B, H, W, E, N = _check_inputs(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, a_log=a_log)
     L = _lib.lib()
     dev, dt = x.device, x.dtype
     with torch.cuda.device(dev):
-        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+        d, keep = _make_desc(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, False, a_log)
         gy = grad_output.contiguous()
         keep.append(gy)
         d.gy = gy.data_ptr()
@@ -174,15 +183,18 @@ def scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False
         # buffer for all six would let the tiny d_D, which autograd may keep as D.grad, pin the
         # large per-pixel storage until the gradients are cleared.)
         npn, en = B * H * W * N, E * N
+        dt_A = torch.float32 if a_log else dt                     # gradients of the fp32 parameter A_log are fp32
         if shared_storage:
             big = torch.empty(3 * npn, dtype=dt, device=dev)
-            small = torch.empty(2 * en + E, dtype=dt, device=dev)
             d_BT, d_BL, d_C = (big[k * npn:(k + 1) * npn].view(B, H, W, N) for k in range(3))
+        else:
+            d_BT, d_BL, d_C = (torch.empty((B, H, W, N), dtype=dt, device=dev) for _ in range(3))
+        if shared_storage and dt_A == dt:
+            small = torch.empty(2 * en + E, dtype=dt, device=dev)
             d_AT, d_AL = (small[k * en:(k + 1) * en].view(E, N) for k in range(2))
             d_D = small[2 * en:]
         else:
-            d_BT, d_BL, d_C = (torch.empty((B, H, W, N), dtype=dt, device=dev) for _ in range(3))
-            d_AT, d_AL = (torch.empty((E, N), dtype=dt, device=dev) for _ in range(2))
+            d_AT, d_AL = (torch.empty((E, N), dtype=dt_A, device=dev) for _ in range(2))
             d_D = torch.empty((E,), dtype=dt, device=dev)
         outs = (torch.empty((B, H, W, E), dtype=dt, device=dev), torch.empty((B, H, W, E), dtype=dt, device=dev),
                 torch.empty((B, H, W, E), dtype=dt, device=dev), d_AT, d_AL, d_BT, d_BL, d_C, d_D)
@@ -213,28 +225,29 @@ def _run(op, *args):
 @torch.library.custom_op("mamba2d_b200::scan_fwd", mutates_args=())
 def scan_fwd_op(x: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, AT: torch.Tensor, AL: torch.Tensor,
                 BT: torch.Tensor, BL: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
-                reverse: bool = False) -> torch.Tensor:
-    return scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+                reverse: bool = False, a_log: bool = False) -> torch.Tensor:
+    return scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, False, a_log)
 
 
 @scan_fwd_op.register_fake
-def _scan_fwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
+def _scan_fwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False, a_log=False):
     return torch.empty_like(x, memory_format=torch.contiguous_format)
 
 
 @torch.library.custom_op("mamba2d_b200::scan_bwd", mutates_args=())
 def scan_bwd_op(x: torch.Tensor, deltaT: torch.Tensor, deltaL: torch.Tensor, AT: torch.Tensor, AL: torch.Tensor,
                 BT: torch.Tensor, BL: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
-                grad_output: torch.Tensor, reverse: bool = False) -> list[torch.Tensor]:
-    return list(scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse, shared_storage=False))
+                grad_output: torch.Tensor, reverse: bool = False, a_log: bool = False) -> list[torch.Tensor]:
+    return list(scan_bwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse, shared_storage=False, a_log=a_log))
 
 
 @scan_bwd_op.register_fake
-def _scan_bwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False):
+def _scan_bwd_fake(x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, reverse=False, a_log=False):
     B, H, W, E = x.shape
     N = AT.shape[1]
     mk = lambda *s: x.new_empty(s)
-    return [mk(B, H, W, E), mk(B, H, W, E), mk(B, H, W, E), mk(E, N), mk(E, N),
+    mkA = (lambda *s: AT.new_empty(s)) if a_log else mk
+    return [mk(B, H, W, E), mk(B, H, W, E), mk(B, H, W, E), mkA(E, N), mkA(E, N),
             mk(B, H, W, N), mk(B, H, W, N), mk(B, H, W, N), mk(E)]
 
 
@@ -363,17 +376,20 @@ def _xproj_wgrad_fake(d_proj, x, d_state, dt_rank):
     return x.new_empty(2 * dt_rank + 3 * d_state, x.shape[-1])
 
 
-_EAGER.update({scan_fwd_op: scan_fwd, scan_bwd_op: lambda *a: list(scan_bwd(*a)), dtproj_fwd_op: _dtproj_fwd,
+_EAGER.update({scan_fwd_op: lambda *a: scan_fwd(*a[:10], False, *a[10:]),
+               scan_bwd_op: lambda *a: list(scan_bwd(*a[:11], True, *a[11:])), dtproj_fwd_op: _dtproj_fwd,
                dtproj_bwd_op: _dtproj_bwd, xproj_wgrad_op: _xproj_wgrad})
 
 
-def _proj_forward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
+def _proj_forward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, want_A=True):
     """``proj_params`` without an autograd graph.  Returns the seven outputs and what the
     hand-written backward needs: (proj, AT32, AL32) -- softplus' is recovered from deltaT / deltaL
-    themselves, so the pre-activations are not kept."""
+    themselves, so the pre-activations are not kept.  Without ``want_A`` the two A outputs are the
+    fp32 parameters A_log themselves (the scan kernels then apply ``-exp`` on their own) and AT32 /
+    AL32 are None."""
     d_state, dt_rank, dt = AT_log.shape[1], dt_projT_w.shape[1], x.dtype
-    AT32 = -torch.exp(AT_log.float())
-    AL32 = -torch.exp(AL_log.float())
+    AT32 = -torch.exp(AT_log.float()) if want_A else None
+    AL32 = -torch.exp(AL_log.float()) if want_A else None
     proj = F.linear(x, x_proj_w)
     rT, rL, BT, BL, C = torch.split(proj, [dt_rank, dt_rank, d_state, d_state, d_state], dim=-1)
     if _fusable(x, proj.shape[-1], dt_rank, proj, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
@@ -381,8 +397,8 @@ def _proj_forward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_
     else:
         deltaT = F.softplus(F.linear(rT, dt_projT_w, dt_projT_b))
         deltaL = F.softplus(F.linear(rL, dt_projL_w, dt_projL_b))
-    out = (deltaT.to(dtype=dt), deltaL.to(dtype=dt), AT32.to(dtype=dt), AL32.to(dtype=dt),
-           BT.to(dtype=dt), BL.to(dtype=dt), C.to(dtype=dt))
+    A_out = (AT32.to(dtype=dt), AL32.to(dtype=dt)) if want_A else (AT_log.float(), AL_log.float())
+    out = (deltaT.to(dtype=dt), deltaL.to(dtype=dt), *A_out, BT.to(dtype=dt), BL.to(dtype=dt), C.to(dtype=dt))
     return out, (proj, AT32, AL32)
 
 
@@ -415,7 +431,9 @@ def _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, 
         d_bT, d_bL = sT.reshape(-1, E).sum(0), sL.reshape(-1, E).sum(0)
         d_wx = d_proj.reshape(-1, d_proj.shape[-1]).t() @ x.reshape(-1, E)
     d_x = d_proj @ x_proj_w.to(d_proj.dtype)
-    d_AT_log = None if d_AT is None else (d_AT.float() * AT32).to(AT_log.dtype)      # d(-exp(a))/da = -exp(a) = A
+    # d(-exp(a))/da = -exp(a) = A.  (Callers that let the scan kernels apply -exp pass None here: the
+    # kernels return d_A_log themselves.)
+    d_AT_log = None if d_AT is None else (d_AT.float() * AT32).to(AT_log.dtype)
     d_AL_log = None if d_AL is None else (d_AL.float() * AL32).to(AL_log.dtype)
     return d_x, d_AT_log, d_AL_log, d_wx, d_wT, d_bT, d_wL, d_bL
 
@@ -444,6 +462,28 @@ class _proj_params_fn(torch.autograd.Function):
         return d_x, d_AT_log, d_AL_log, d_wx, d_wT, d_bT, d_wL, d_bL
 
 
+class _proj5_fn(torch.autograd.Function):
+    """The input-dependent outputs of ``proj_params`` only (deltaT, deltaL, BT, BL, C): what the entry
+    uses when the scan kernels take A_log directly."""
+
+    @staticmethod
+    def forward(ctx, x, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, A_like):
+        out, saved = _proj_forward(x, A_like, A_like, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, want_A=False)
+        out = (out[0], out[1], out[4], out[5], out[6])
+        if torch.compiler.is_compiling():
+            out = tuple(t.clone() for t in out)       # see _proj_params_fn.forward
+        ctx.save_for_backward(x, x_proj_w, dt_projT_w, dt_projL_w, out[0], out[1], saved[0], A_like)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_dT, d_dL, d_BT, d_BL, d_C):
+        x, x_proj_w, dt_projT_w, dt_projL_w, deltaT, deltaL, proj, A_like = ctx.saved_tensors
+        g = _proj_backward(x, A_like, A_like, x_proj_w, dt_projT_w, dt_projL_w, deltaT, deltaL, (proj, None, None),
+                           d_dT, d_dL, None, None, d_BT, d_BL, d_C)
+        d_x, _, _, d_wx, d_wT, d_bT, d_wL, d_bL = g
+        return d_x, d_wx, d_wT, d_bT, d_wL, d_bL, None
+
+
 def proj_params(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b):
     """Input-dependent scan parameters from x (B,H,W,E).
 
@@ -459,33 +499,35 @@ def proj_params(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w,
 
 class wf_cuda_fn_pr(torch.autograd.Function):
     """Partial recomputation: projections are computed once and saved; the hidden state is
-    recomputed inside the backward kernel."""
+    recomputed inside the backward kernel.  With ``a_log`` the ``AT`` / ``AL`` arguments are the fp32
+    parameters A_log and their gradients are gradients with respect to A_log."""
 
     @staticmethod
-    def forward(ctx, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False):
-        y = _run(scan_fwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+    def forward(ctx, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse=False, a_log=False):
+        y = _run(scan_fwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, a_log)
         ctx.save_for_backward(x, deltaT, deltaL, AT, AL, BT, BL, C, D)
-        ctx.reverse = bool(reverse)
+        ctx.reverse, ctx.a_log = bool(reverse), bool(a_log)
         return y
 
     @staticmethod
     def backward(ctx, grad_output):
         x, deltaT, deltaL, AT, AL, BT, BL, C, D = ctx.saved_tensors
-        grads = _run(scan_bwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output.to(x.dtype), ctx.reverse)
-        return (*grads, None)
+        grads = _run(scan_bwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output.to(x.dtype), ctx.reverse, ctx.a_log)
+        return (*grads, None, None)
 
 
 class wf_cuda_fn_fr(torch.autograd.Function):
     """Full recomputation: only x and the weights are saved; the projections are recomputed in
     backward.  The reference recomputes them under autograd and calls ``torch.autograd.grad``
-    (wavefront_cuda.py:235-302); here their backward is written out (``_proj_backward``)."""
+    (wavefront_cuda.py:235-302); here their backward is written out (``_proj_backward``).  The scan
+    kernels take A_log directly, so neither pass computes ``-exp(A_log)`` in PyTorch."""
 
     @staticmethod
     def forward(ctx, x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, reverse=False):
         with torch.no_grad():
             (deltaT, deltaL, AT, AL, BT, BL, C), _ = _proj_forward(
-                x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
-        y = _run(scan_fwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+                x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, want_A=False)
+        y = _run(scan_fwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, True)
         ctx.reverse = bool(reverse)
         ctx.save_for_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D)
         return y
@@ -496,13 +538,13 @@ class wf_cuda_fn_fr(torch.autograd.Function):
         grad_output = grad_output.to(x.dtype)
         with torch.no_grad():
             (deltaT, deltaL, AT, AL, BT, BL, C), saved = _proj_forward(
-                x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
-            d_x_scan, d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C, d_D = _run(scan_bwd_op, 
-                x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, ctx.reverse)
+                x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, want_A=False)
+            d_x_scan, d_dT, d_dL, d_AT_log, d_AL_log, d_BT, d_BL, d_C, d_D = _run(
+                scan_bwd_op, x, deltaT, deltaL, AT, AL, BT, BL, C, D, grad_output, ctx.reverse, True)
             g = _proj_backward(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projL_w, deltaT, deltaL, saved,
-                               d_dT, d_dL, d_AT, d_AL, d_BT, d_BL, d_C)
+                               d_dT, d_dL, None, None, d_BT, d_BL, d_C)
         d_x = d_x_scan + g[0]
-        return (d_x, *g[1:], d_D, None)
+        return (d_x, d_AT_log.to(AT_log.dtype), d_AL_log.to(AL_log.dtype), *g[3:], d_D, None)
 
 
 def wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, recomp="partial",
@@ -543,12 +585,13 @@ def wavefront_scan_cuda(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_
     if act_out == "gelu" and not (torch.is_grad_enabled() and any(t.requires_grad for t in params)) \
             and not torch.compiler.is_compiling():
         # nothing to differentiate: one kernel for scan + activation
-        (deltaT, deltaL, AT, AL, BT, BL, C), _ = _proj_forward(*params[:-1])
-        return scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, gelu_out=True)
+        (deltaT, deltaL, AT, AL, BT, BL, C), _ = _proj_forward(*params[:-1], want_A=False)
+        return scan_fwd(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse, gelu_out=True, a_log=True)
     if recomp == "partial":
-        deltaT, deltaL, AT, AL, BT, BL, C = proj_params(
-            x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b)
-        y = wf_cuda_fn_pr.apply(x, deltaT, deltaL, AT, AL, BT, BL, C, D, reverse)
+        # the scan kernels take A_log directly (A = -exp(A_log) and its gradient are applied inside
+        # them), so only the input-dependent projections are computed here
+        deltaT, deltaL, BT, BL, C = _proj5_fn.apply(x, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, AT_log)
+        y = wf_cuda_fn_pr.apply(x, deltaT, deltaL, AT_log.float(), AL_log.float(), BT, BL, C, D, reverse, True)
     else:
         y = wf_cuda_fn_fr.apply(x, AT_log, AL_log, x_proj_w, dt_projT_w, dt_projT_b, dt_projL_w, dt_projL_b, D, reverse)
     return F.gelu(y) if act_out == "gelu" else y

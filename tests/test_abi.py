@@ -61,7 +61,8 @@ def test_descriptor_validation_without_a_device(L):
     assert L.m2d_scan_fwd(ctypes.byref(_desc(dtype=7)), None) == -2
     assert L.m2d_scan_fwd(ctypes.byref(_desc(C_pitch=8)), None) == -5
     assert L.m2d_scan_fwd(ctypes.byref(_desc(struct_bytes=8)), None) == -8
-    assert L.m2d_scan_fwd(ctypes.byref(_desc(flags=4)), None) == -10   # unknown flag bit
+    assert L.m2d_scan_fwd(ctypes.byref(_desc(flags=8)), None) == -10   # unknown flag bit
+    assert L.m2d_scan_bwd(ctypes.byref(_desc(flags=_lib.M2D_SCAN_A_LOG)), None) == -1     # known to both entries
     assert L.m2d_scan_fwd(ctypes.byref(_desc(flags=_lib.M2D_SCAN_GELU_OUT)), None) == -1   # forward-only bit: next check
     assert L.m2d_scan_bwd(ctypes.byref(_desc(flags=_lib.M2D_SCAN_GELU_OUT)), None) == -10  # ... the backward refuses it
     assert L.m2d_scan_bwd(ctypes.byref(_desc(flags=_lib.M2D_SCAN_REVERSE)), None) == -1   # known bit: next check

@@ -17,8 +17,8 @@ def test_public_signature_matches_reference_entry():
                          "dt_projL_b", "D", "recomp", "scan_start", "act_out"]
     assert sig["recomp"].default == "partial" and sig["scan_start"].default == "TL" and sig["act_out"].default is None
     pr = inspect.signature(wc.wf_cuda_fn_pr.forward).parameters
-    assert list(pr)[1:] == ["x", "deltaT", "deltaL", "AT", "AL", "BT", "BL", "C", "D", "reverse"]
-    assert pr["reverse"].default is False
+    assert list(pr)[1:] == ["x", "deltaT", "deltaL", "AT", "AL", "BT", "BL", "C", "D", "reverse", "a_log"]
+    assert pr["reverse"].default is False and pr["a_log"].default is False
     assert list(inspect.signature(wc.proj_params).parameters) == \
         ["x", "AT_log", "AL_log", "x_proj_w", "dt_projT_w", "dt_projT_b", "dt_projL_w", "dt_projL_b"]
 

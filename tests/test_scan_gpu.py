@@ -165,3 +165,30 @@ def test_forward_with_output_gelu(kind, reverse):
     got = scan_fwd(*[d[k] for k in ORDER], reverse=reverse, gelu_out=True)
     torch.cuda.synchronize()
     assert rel_err(got.float().cpu().numpy(), want) < TOL[kind]
+
+
+@pytest.mark.parametrize("kind", ["f32", "bf16"])
+def test_a_log_inside_the_kernels(kind):
+    """AT / AL given as the fp32 parameters A_log: same y and gradients as with A = -exp(A_log) computed
+    outside (rounded to the I/O type, as the reference's cast does), and d_A_log = d_A * A in fp32."""
+    from mamba2d_b200 import scan_bwd, scan_fwd
+    inp = inputs.make_inputs(3, 15, 11, 64, 16, seed=41)
+    d = to_dev(inp, TDT[kind])
+    g = torch.Generator().manual_seed(5)
+    AT_log = (torch.rand(64, 16, generator=g) * 2.5).cuda()
+    AL_log = (torch.rand(64, 16, generator=g) * 2.5).cuda()
+    AT32, AL32 = -torch.exp(AT_log), -torch.exp(AL_log)
+    a_out = dict(d, AT=AT32.to(TDT[kind]), AL=AL32.to(TDT[kind]))
+    a_in = dict(d, AT=AT_log, AL=AL_log)
+    y0 = scan_fwd(*[a_out[k] for k in ORDER])
+    y1 = scan_fwd(*[a_in[k] for k in ORDER], a_log=True)
+    g0 = scan_bwd(*[a_out[k] for k in ORDER], d["gy"])
+    g1 = scan_bwd(*[a_in[k] for k in ORDER], d["gy"], a_log=True)
+    torch.cuda.synchronize()
+    tol = 1e-5 if kind == "f32" else 1e-2
+    assert rel_err(y1.float().cpu().numpy(), y0.float().cpu().numpy()) < tol
+    for name, u, v in zip(GRADS, g1, g0):
+        if name in ("d_AT", "d_AL"):
+            assert u.dtype == torch.float32
+            v = v.float() * (AT32 if name == "d_AT" else AL32)
+        assert rel_err(u.float().cpu().numpy(), v.float().cpu().numpy()) < tol, name
