@@ -50,6 +50,24 @@ __device__ __forceinline__ void stcg_if(bool on, float4* p, const float4& v) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t@p st.global.cg.v4.f32 [%0], {%1, %2, %3, %4};\n\t}"
                  ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"((int)on) : "memory");
 }
+// Unpredicated forms, for call sites that branch on a loop-invariant condition themselves.
+__device__ __forceinline__ void cp_async16(unsigned smem_addr, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async8(unsigned smem_addr, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_addr), "l"(gmem) : "memory");
+}
+// A 2 KiB (four 16-byte pieces per lane, 512 bytes apart) or 1 KiB (two pieces) block.
+__device__ __forceinline__ void cp_async_block(unsigned smem_addr, const void* gmem, bool half) {
+    if (half) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n\tcp.async.cg.shared.global [%0+512], [%1+512], 16;"
+                     ::"r"(smem_addr), "l"(gmem) : "memory");
+    } else {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n\tcp.async.cg.shared.global [%0+512], [%1+512], 16;\n\t"
+                     "cp.async.cg.shared.global [%0+1024], [%1+1024], 16;\n\tcp.async.cg.shared.global [%0+1536], [%1+1536], 16;"
+                     ::"r"(smem_addr), "l"(gmem) : "memory");
+    }
+}
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 
 // Four 16-byte copies under one predicate: a 2 KiB (cell, warp) block, 512 bytes apart on both sides.
@@ -140,6 +158,19 @@ struct LaneCopy {
         bpitch = tb == 0 ? pBT : (tb == 1 ? pBL : pC);
         b_on = (lane < 12) && (pb * 4 < N);
         bbase = static_cast<const char*>(bp) + (size_t)(pb * 4) * sizeof(io_t);
+    }
+    // Same as issue() below with ordinary branches on the two lane-invariant conditions (the
+    // compiler keeps them as predicates across a loop instead of re-deriving them per copy).
+    __device__ __forceinline__ void issue_plain(unsigned stage_addr, int lane, int pix, int E) const {
+        const char* src_c = cbase + (size_t)(pix * E) * sizeof(io_t);
+        const char* src_b = bbase + (size_t)(pix * bpitch) * sizeof(io_t);
+        if (sizeof(io_t) == 4) {
+            if (c_on) cp_async16(stage_addr + lane * 16, src_c);
+            if (b_on) cp_async16(stage_addr + (32 + lane) * 16, src_b);
+        } else {
+            if (c_on) cp_async8(stage_addr + lane * 16, src_c);
+            if (b_on) cp_async8(stage_addr + (32 + lane) * 16, src_b);
+        }
     }
     // stage_addr: shared-space address of the stage (this parity); pix: flat pixel index.
     __device__ __forceinline__ void issue(unsigned stage_addr, int lane, int pix, int E) const {

@@ -1,10 +1,13 @@
 // Forward entry point of the wavefront scan: one fused kernel, y written directly.
 #include "launch.cuh"
+#include "sweep_rows.cuh"
 
 namespace m2d {
 
-template <typename io_t, bool VEC, bool CHAINED, int CB>
-__global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
+// Several CTAs per image (large maps, few images): the flat step loop with the cross-CTA hand-off.
+template <typename io_t, bool VEC>
+__global__ void __launch_bounds__(256, 2) m2d_fwd_chained_kernel(const FwdArgs a) {
+    constexpr int CB = 1;
     extern __shared__ float4 handoff[];
     const int lane = threadIdx.x & 31;
     const int cq = lane >> 2, nq = lane & 3;
@@ -27,7 +30,30 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
     const int chains = (int)gridDim.x / a.chain;
     const int chain_id = (int)blockIdx.x / a.chain, cpos = (int)blockIdx.x % a.chain;
     const int nb = (a.B - chain_id + chains - 1) / chains;
-    forward_sweep<io_t, VEC, false, CHAINED, CB>(a, handoff, params, D_own, chain_id, chains, nb, cpos, a.chain);
+    forward_sweep<io_t, VEC, false, true, CB>(a, handoff, params, D_own, chain_id, chains, nb, cpos, a.chain);
+}
+
+// Batch mode (one CTA per image and channel group): the sweep written as nested loops.
+template <typename io_t, bool VEC>
+__global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
+    constexpr int CB = 1;
+    extern __shared__ float4 handoff[];
+    const int lane = threadIdx.x & 31;
+    const int cq = lane >> 2, nq = lane & 3;
+    const int g = blockIdx.y;
+    const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
+    const int chv = min(4, max(0, a.E - ch0));
+    const int nv = min(4, max(0, a.N - n0));
+    const int total = (int)(sweep_smem_bytes(blockDim.x >> 5, CB) / sizeof(float4));
+    for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int ch_own = g * kGroup + lane;
+    const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
+    __syncthreads();
+    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes((blockDim.x >> 5), CB));
+    if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane, a.a_log);
+    __syncthreads();
+    const int nb = (a.B - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    forward_rows<io_t, VEC, false, CB>(a, handoff, params, D_own, blockIdx.x, gridDim.x, nb);
 }
 
 template <typename io_t>
@@ -48,15 +74,9 @@ static int launch_fwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
         zero_bytes = kStatusBytes + nband * sizeof(int);
     }
     if (cudaMemsetAsync(ws, 0, zero_bytes, st) != cudaSuccess) return M2D_ERR_LAUNCH;
-    void (*kern)(const FwdArgs);
-    if (pl.cb == 2) {
-        kern = pl.chain > 1 ? (vec ? m2d_fwd_kernel<io_t, true, true, 2> : m2d_fwd_kernel<io_t, false, true, 2>)
-                            : (vec ? m2d_fwd_kernel<io_t, true, false, 2> : m2d_fwd_kernel<io_t, false, false, 2>);
-    } else {
-        kern = pl.chain > 1 ? (vec ? m2d_fwd_kernel<io_t, true, true, 1> : m2d_fwd_kernel<io_t, false, true, 1>)
-                            : (vec ? m2d_fwd_kernel<io_t, true, false, 1> : m2d_fwd_kernel<io_t, false, false, 1>);
-    }
-    return launch_sweep_kernel(kern, a, pl, (d->W + pl.cb - 1) / pl.cb, st);
+    void (*kern)(const FwdArgs) = pl.chain > 1 ? (vec ? m2d_fwd_chained_kernel<io_t, true> : m2d_fwd_chained_kernel<io_t, false>)
+                                               : (vec ? m2d_fwd_kernel<io_t, true> : m2d_fwd_kernel<io_t, false>);
+    return launch_sweep_kernel(kern, a, pl, d->W, st);
 }
 
 }  // namespace m2d

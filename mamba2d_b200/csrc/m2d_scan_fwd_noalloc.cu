@@ -25,6 +25,7 @@
 #include <mutex>
 
 #include "launch.cuh"
+#include "sweep_rows.cuh"
 
 namespace m2d {
 
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_noalloc_kernel(const ScanArgs 
     if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane, a.a_log);
     __syncthreads();
     const int nb = (a.B - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    forward_sweep<io_t, VEC, false>(a, handoff, params, D_own, blockIdx.x, gridDim.x, nb);
+    forward_rows<io_t, VEC, false, 1>(a, handoff, params, D_own, blockIdx.x, gridDim.x, nb);
 }
 
 template <typename io_t>
@@ -93,14 +94,14 @@ static int launch_noalloc(const m2d_scan_desc* d, const Plan& pl, bool vec, floa
 
 extern "C" uint64_t m2d_scan_fwd_noalloc_need(const m2d_scan_desc* d) {
     if (m2d::check_desc(d, false, false) != M2D_OK) return 0;
-    return m2d::plan_fwd(d, false, false).scratch;
+    return m2d::plan_fwd(d, false).scratch;
 }
 
 extern "C" int m2d_scan_fwd_noalloc(const m2d_scan_desc* d, void* stream) {
     int rc = m2d::check_desc(d, false, true);
     if (rc != M2D_OK) return rc;
     if (!d->y) return M2D_ERR_NULL;
-    const m2d::Plan pl = m2d::plan_fwd(d, false, false);   // one CTA per image: the fixed array holds per-CTA rings only
+    const m2d::Plan pl = m2d::plan_fwd(d, false);   // one CTA per image: the fixed array holds per-CTA rings only
     if (pl.scratch > M2D_NOALLOC_SCRATCH_BYTES) return M2D_ERR_TOO_LARGE;   // decided before any device work
     float4* ring = nullptr;
     rc = m2d::ring_address(&ring);

@@ -144,7 +144,7 @@ inline int bound_chain(long long want, int nbands, int steps_per_row, int Rb) {
     return want < 1 ? 1 : (int)want;
 }
 
-inline Plan plan_fwd(const m2d_scan_desc* d, bool allow_chain = true, bool allow_cb = true) {
+inline Plan plan_fwd(const m2d_scan_desc* d, bool allow_chain = true) {
     Plan p = plan_best(d, 8, 16, 1);
     // Few images on a large map: give every image a chain of CTAs, each owning every chain-th band,
     // so that the bands of one image run as a pipeline across SMs.  All CTAs must be resident.
@@ -152,11 +152,6 @@ inline Plan plan_fwd(const m2d_scan_desc* d, bool allow_chain = true, bool allow
     const long long ctas = (long long)p.grid_x * p.groups;
     if (allow_chain && p.nbands > 1 && ctas * 2 <= slots)
         p.chain = bound_chain(slots / ctas, p.nbands, (d->W + p.cb - 1) / p.cb, p.Rb);
-    if (p.chain == 1 && allow_cb && d->W >= 24) {
-        // batch mode: two cells per step where rows are long enough for the band hand-off to stay
-        // a step ahead (measured 7 % faster at 56x56 and 28x28; chained launches prefer finer steps)
-        p = plan_best(d, 8, 16, 2);
-    }
     p.scratch = kStatusBytes;
     if (p.chain > 1) {
         const size_t nband = (size_t)d->B * p.groups * p.nbands;
