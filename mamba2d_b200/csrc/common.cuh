@@ -223,6 +223,23 @@ __device__ __forceinline__ float reduce_states(float v0, float v1, float v2, flo
     return k + __shfl_xor_sync(0xffffffffu, s, 1);
 }
 
+// The per-(channel,state) parameters A*log2(e) of the CTA's 32 channels live in shared memory
+// behind everything else: [AT | AL][4 channels][32 lanes] float4 (4 KiB), read block by block.
+constexpr int kParamF4 = 2 * 4 * 32;
+
+// Shared memory of the nested-loop sweeps, in this order (the parameters follow):
+//   pull    3 x 2 KiB           ring blocks for the warp that leads a band
+//   slots   warps x 2 x 2 KiB   hand-off: warp (rank) k writes slot k, the next one reads it
+//   stage   warps x 3 x kStageBytes
+//   harea   backward only: (warps + 1) x 3 x 2 KiB state blocks for the adjoint sweep
+__host__ __device__ inline size_t rows_handoff_f4(int warps) { return (size_t)(3 + 2 * warps) * kSlotF4; }
+__host__ __device__ inline size_t rows_fwd_smem_bytes(int warps) {
+    return rows_handoff_f4(warps) * sizeof(float4) + (size_t)warps * 3 * kStageBytes;
+}
+__host__ __device__ inline size_t rows_bwd_smem_bytes(int warps) {
+    return rows_fwd_smem_bytes(warps) + (size_t)(warps + 1) * 3 * kSlotF4 * sizeof(float4);
+}
+
 // Host-side launch plan shared by the workspace queries and the launches.
 struct Plan {
     int groups;        // ceil(E / 32)
@@ -231,7 +248,8 @@ struct Plan {
     int nbands;        // ceil(H / Rb)
     int grid_x;        // image chains per channel group; chain k walks images k, k + grid_x, ...
     int cb;            // cells per step and warp (forward only)
-    int chain;         // CTAs per chain (forward only; > 1 when there are far fewer images than SMs)
+    int chain;         // CTAs per chain (> 1 when there are far fewer images than SMs)
+    bool rows;         // batch mode with the nested-loop kernel (its own shared-memory layout)
     size_t smem;       // dynamic shared memory per CTA
     size_t scratch;    // workspace bytes
 };

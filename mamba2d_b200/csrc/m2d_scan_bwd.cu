@@ -66,6 +66,12 @@ inline Plan plan_bwd(const m2d_scan_desc* d) {
         const long long ctas = (long long)p.grid_x * p.groups;
         if (p.nbands > 1 && ctas * 2 <= slots) p.chain = bound_chain(slots / ctas, p.nbands, d->W, p.Rb);
     }
+    if (p.chain == 1 && d->W >= 3) {
+        // batch mode: the nested-loop kernel (maps narrower than three columns keep the flat one)
+        p = plan_best(d, maxw, 2 * M2D_BWD_MAXW, 1, 2);
+        p.rows = true;
+        p.smem = rows_bwd_smem_bytes(p.warps) + kParamF4 * sizeof(float4);
+    }
     p.scratch = bwd_layout(d, p).total;
     return p;
 }
@@ -160,7 +166,7 @@ __global__ void __launch_bounds__(M2D_BWD_MAXW * 32, 2) m2d_bwd_chained_kernel(c
 // Batch mode (one CTA per image and channel group): both sweeps written as nested loops.
 template <typename io_t, bool VEC>
 __global__ void __launch_bounds__(M2D_BWD_MAXW * 32, 2) m2d_bwd_kernel(const ScanArgs a) {
-    extern __shared__ float4 handoff[];
+    extern __shared__ float4 smem[];
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
@@ -169,8 +175,8 @@ __global__ void __launch_bounds__(M2D_BWD_MAXW * 32, 2) m2d_bwd_kernel(const Sca
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
 
-    const int total = (int)(bwd_smem_bytes(nwarps) / sizeof(float4));
-    for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int total = (int)(rows_bwd_smem_bytes(nwarps) / sizeof(float4));
+    for (int k = threadIdx.x; k < total; k += blockDim.x) smem[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 
     const int ch_own = g * kGroup + lane;
     const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
@@ -182,19 +188,19 @@ __global__ void __launch_bounds__(M2D_BWD_MAXW * 32, 2) m2d_bwd_kernel(const Sca
         for (int n = 0; n < 4; ++n) dAT[c][n] = dAL[c][n] = 0.f;
     }
     __syncthreads();
-    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + bwd_smem_bytes(nwarps));
+    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(smem) + rows_bwd_smem_bytes(nwarps));
     if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane, a.a_log);
     __syncthreads();
 
     for (int b = (int)blockIdx.x; b < a.B; b += (int)gridDim.x) {
-        forward_rows<io_t, VEC, true, 1>(a, handoff, params, D_own, b, 0, 1);
-        reverse_rows<io_t, VEC>(a, handoff, params, D_own, dAT, dAL, dD, b);
+        forward_rows<io_t, VEC, true>(a, smem, params, D_own, b, 0, 1);
+        reverse_rows<io_t, VEC>(a, smem, params, D_own, dAT, dAL, dD, b);
     }
 
     // ---- per-(channel,state) sums: fold the CTA's row-warps through shared memory, then one
     //      atomic per value from warp 0 ----------------------------------------------------------
-    float* red = reinterpret_cast<float*>(handoff);     // reuse: needs 36 floats per thread
-    const int slot = 2 * (nwarps + 1) * kSlotF4 * 4;     // floats available
+    float* red = reinterpret_cast<float*>(smem);        // reuse: needs 36 floats per thread
+    const int slot = (int)rows_handoff_f4(nwarps) * 4;   // floats available
     const bool fits = (int)blockDim.x * 36 <= slot;
     if (fits && nwarps > 1) {
         float* mine = red + (size_t)threadIdx.x * 36;
@@ -311,8 +317,9 @@ static int launch_bwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
         a.accAT = acc + 3 * npn; a.accAL = a.accAT + en; a.accD = a.accAL + en;
         if (cudaMemsetAsync(acc, 0, L.acc_bytes, st) != cudaSuccess) return M2D_ERR_LAUNCH;
     }
-    void (*kern)(const ScanArgs) = pl.chain > 1 ? (vec ? m2d_bwd_chained_kernel<io_t, true> : m2d_bwd_chained_kernel<io_t, false>)
-                                                : (vec ? m2d_bwd_kernel<io_t, true> : m2d_bwd_kernel<io_t, false>);
+    // (the flat kernel with a chain of one CTA is the fallback for maps the nested-loop kernel does not take)
+    void (*kern)(const ScanArgs) = pl.rows ? (vec ? m2d_bwd_kernel<io_t, true> : m2d_bwd_kernel<io_t, false>)
+                                           : (vec ? m2d_bwd_chained_kernel<io_t, true> : m2d_bwd_chained_kernel<io_t, false>);
     const int rc = launch_sweep_kernel(kern, a, pl, d->W, st);
     if (rc != M2D_OK) return rc;
     if (d->dtype != M2D_F32) {

@@ -36,24 +36,24 @@ __global__ void __launch_bounds__(256, 2) m2d_fwd_chained_kernel(const FwdArgs a
 // Batch mode (one CTA per image and channel group): the sweep written as nested loops.
 template <typename io_t, bool VEC>
 __global__ void __launch_bounds__(256, 2) m2d_fwd_kernel(const FwdArgs a) {
-    constexpr int CB = 1;
-    extern __shared__ float4 handoff[];
+    extern __shared__ float4 smem[];
     const int lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
     const int g = blockIdx.y;
     const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
-    const int total = (int)(sweep_smem_bytes(blockDim.x >> 5, CB) / sizeof(float4));
-    for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int total = (int)(rows_fwd_smem_bytes(nwarps) / sizeof(float4));
+    for (int k = threadIdx.x; k < total; k += blockDim.x) smem[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     const int ch_own = g * kGroup + lane;
     const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
     __syncthreads();
-    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes((blockDim.x >> 5), CB));
+    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(smem) + rows_fwd_smem_bytes(nwarps));
     if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane, a.a_log);
     __syncthreads();
     const int nb = (a.B - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    forward_rows<io_t, VEC, false, CB>(a, handoff, params, D_own, blockIdx.x, gridDim.x, nb);
+    forward_rows<io_t, VEC, false>(a, smem, params, D_own, blockIdx.x, gridDim.x, nb);
 }
 
 template <typename io_t>
@@ -74,8 +74,9 @@ static int launch_fwd(const m2d_scan_desc* d, const Plan& pl, bool vec, cudaStre
         zero_bytes = kStatusBytes + nband * sizeof(int);
     }
     if (cudaMemsetAsync(ws, 0, zero_bytes, st) != cudaSuccess) return M2D_ERR_LAUNCH;
-    void (*kern)(const FwdArgs) = pl.chain > 1 ? (vec ? m2d_fwd_chained_kernel<io_t, true> : m2d_fwd_chained_kernel<io_t, false>)
-                                               : (vec ? m2d_fwd_kernel<io_t, true> : m2d_fwd_kernel<io_t, false>);
+    // (the flat kernel with a chain of one CTA is the fallback for maps the nested-loop kernel does not take)
+    void (*kern)(const FwdArgs) = pl.rows ? (vec ? m2d_fwd_kernel<io_t, true> : m2d_fwd_kernel<io_t, false>)
+                                          : (vec ? m2d_fwd_chained_kernel<io_t, true> : m2d_fwd_chained_kernel<io_t, false>);
     return launch_sweep_kernel(kern, a, pl, d->W, st);
 }
 

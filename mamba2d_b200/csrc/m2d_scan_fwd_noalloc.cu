@@ -54,25 +54,29 @@ static int ring_address(float4** out) {
     return M2D_OK;
 }
 
-template <typename io_t, bool VEC>
+// ROWS: the nested-loop sweep; otherwise the flat step loop (maps narrower than three columns).
+template <typename io_t, bool VEC, bool ROWS>
 __global__ void __launch_bounds__(256, 2) m2d_fwd_noalloc_kernel(const ScanArgs a) {
-    extern __shared__ float4 handoff[];
+    extern __shared__ float4 smem[];
     const int lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
     const int g = blockIdx.y;
     const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
-    const int total = (int)(sweep_smem_bytes(blockDim.x >> 5) / sizeof(float4));
-    for (int k = threadIdx.x; k < total; k += blockDim.x) handoff[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const size_t bytes = ROWS ? rows_fwd_smem_bytes(nwarps) : sweep_smem_bytes(nwarps);
+    const int total = (int)(bytes / sizeof(float4));
+    for (int k = threadIdx.x; k < total; k += blockDim.x) smem[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     const int ch_own = g * kGroup + lane;
     const float D_own = ch_own < a.E ? load1(static_cast<const io_t*>(a.D), ch_own) : 0.f;
     __syncthreads();
-    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes((blockDim.x >> 5)));
+    float4* const params = reinterpret_cast<float4*>(reinterpret_cast<char*>(smem) + bytes);
     if (threadIdx.x < 32) stage_params<io_t>(params, a.AT, a.AL, a.N, ch0, chv, n0, nv, lane, a.a_log);
     __syncthreads();
     const int nb = (a.B - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    forward_rows<io_t, VEC, false, 1>(a, handoff, params, D_own, blockIdx.x, gridDim.x, nb);
+    if (ROWS) forward_rows<io_t, VEC, false>(a, smem, params, D_own, blockIdx.x, gridDim.x, nb);
+    else forward_sweep<io_t, VEC, false, false, 1>(a, smem, params, D_own, blockIdx.x, gridDim.x, nb);
 }
 
 template <typename io_t>
@@ -86,7 +90,8 @@ static int launch_noalloc(const m2d_scan_desc* d, const Plan& pl, bool vec, floa
     a.ring = reinterpret_cast<float4*>(base + kStatusBytes);
     a.chain = 1;
     if (cudaMemsetAsync(base, 0, sizeof(int), st) != cudaSuccess) return M2D_ERR_LAUNCH;
-    void (*kern)(const ScanArgs) = vec ? m2d_fwd_noalloc_kernel<io_t, true> : m2d_fwd_noalloc_kernel<io_t, false>;
+    void (*kern)(const ScanArgs) = pl.rows ? (vec ? m2d_fwd_noalloc_kernel<io_t, true, true> : m2d_fwd_noalloc_kernel<io_t, false, true>)
+                                           : (vec ? m2d_fwd_noalloc_kernel<io_t, true, false> : m2d_fwd_noalloc_kernel<io_t, false, false>);
     return launch_sweep_kernel(kern, a, pl, d->W, st);
 }
 

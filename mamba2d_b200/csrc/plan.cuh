@@ -80,17 +80,20 @@ inline int pick_warps(int H, int max_warps) {
     return best;
 }
 
-inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int warps_per_sm, int cb = 1) {
+// `lead`: how many steps before the band below reads a boundary block it must have been written (1 for
+// the flat step loops, 2 for the nested-loop sweeps, which request everything two steps ahead).
+inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int warps_per_sm, int cb = 1, int lead = 1) {
     Plan p;
     p.cb = cb;
+    p.rows = false;
     p.groups = (d->E + kGroup - 1) / kGroup;
     p.warps = pick_warps(d->H, max_warps);
     p.Rb = p.warps;
     p.nbands = (d->H + p.Rb - 1) / p.Rb;
     const int nch = (d->W + cb - 1) / cb;    // steps per row
-    if (p.nbands > 1 && p.Rb > nch - 1) {
-        // a band boundary must be written at least one step before the next band reads it
-        p.Rb = nch - 1;
+    if (p.nbands > 1 && p.Rb > nch - lead) {
+        // a band boundary must be written at least `lead` steps before the next band reads it
+        p.Rb = nch - lead > 1 ? nch - lead : 1;
         p.warps = p.Rb;
         p.nbands = (d->H + p.Rb - 1) / p.Rb;
     }
@@ -109,12 +112,12 @@ inline Plan plan_common(const m2d_scan_desc* d, int max_warps, int warps_per_sm,
 
 // Try every cap on the row-warps per CTA and keep the plan that keeps the most warps resident,
 // discounted by the rows lost to padding; ties go to the larger CTA.
-inline Plan plan_best(const m2d_scan_desc* d, int max_warps, int warps_per_sm, int cb = 1) {
-    Plan best = plan_common(d, max_warps, warps_per_sm, cb);
+inline Plan plan_best(const m2d_scan_desc* d, int max_warps, int warps_per_sm, int cb = 1, int lead = 1) {
+    Plan best = plan_common(d, max_warps, warps_per_sm, cb, lead);
     double best_score = -1.0;
     const double cap = (double)warps_per_sm * sm_count();
     for (int w = max_warps; w >= 2; --w) {
-        const Plan p = plan_common(d, w, warps_per_sm, cb);
+        const Plan p = plan_common(d, w, warps_per_sm, cb, lead);
         double resident = (double)p.grid_x * p.groups * p.warps;
         if (resident > cap) resident = cap;
         const double eff = (double)d->H / ((double)p.nbands * p.Rb);
@@ -152,6 +155,12 @@ inline Plan plan_fwd(const m2d_scan_desc* d, bool allow_chain = true) {
     const long long ctas = (long long)p.grid_x * p.groups;
     if (allow_chain && p.nbands > 1 && ctas * 2 <= slots)
         p.chain = bound_chain(slots / ctas, p.nbands, (d->W + p.cb - 1) / p.cb, p.Rb);
+    if (p.chain == 1 && d->W >= 3) {
+        // batch mode: the nested-loop kernel (maps narrower than three columns keep the flat one)
+        p = plan_best(d, 8, 16, 1, 2);
+        p.rows = true;
+        p.smem = rows_fwd_smem_bytes(p.warps) + kParamF4 * sizeof(float4);
+    }
     p.scratch = kStatusBytes;
     if (p.chain > 1) {
         const size_t nband = (size_t)d->B * p.groups * p.nbands;

@@ -76,9 +76,6 @@ template <typename io_t> struct HsBlock { static constexpr int f4 = sizeof(io_t)
 
 // Dynamic shared memory of a sweep: the hand-off slots followed by one input stage per warp.
 __host__ __device__ inline size_t sweep_smem_bytes(int warps, int cb = 1) { return handoff_bytes(warps, cb) + (size_t)warps * 2 * cb * kStageBytes; }
-// The per-(channel,state) parameters A*log2(e) of the CTA's 32 channels live in shared memory
-// behind everything else: [AT | AL][4 channels][32 lanes] float4 (4 KiB), read block by block.
-constexpr int kParamF4 = 2 * 4 * 32;
 // Element (e, n) of AT / AL as a float.  With `a_log` the tensors hold the fp32 parameter A_log and
 // A = -exp(A_log), rounded to the I/O type the way the reference's cast does
 // (models/kernels/wavefront_cuda.py:72-73, :89-90); `exact` skips that rounding (used for the

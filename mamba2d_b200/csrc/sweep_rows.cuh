@@ -1,40 +1,50 @@
-// Forward wavefront sweep, batch mode (one CTA per image and channel group), written as nested loops.
+// Wavefront sweeps of the batch mode (one CTA per image and channel group), written as nested loops.
 //
-// Same algorithm, data layout, shared-memory layout and block barriers as forward_sweep in
-// sweep_fwd.cuh -- warp r owns row q*Rb + r of band q and lags r steps behind warp 0; one
-// __syncthreads per step -- but every warp walks its own sequence "for each (image, band): for each
-// chunk of the row" instead of decoding a flat step counter: all per-row decisions (row 0, pull from
-// the ring, push to the ring, output offsets) are taken once per row, and the loop over the chunks of
-// a row carries only running indices.  Every warp executes the same number of barriers: r idle steps
-// first, one step that only stages its first chunk, one step per chunk of every (image, band) item --
-// barrier-only steps where the band has no row for this warp -- and Rb-1-r idle steps at the end.
+// Same algorithm and data layout as forward_sweep / reverse_sweep in sweep_fwd.cuh / sweep_bwd.cuh --
+// warp r owns row q*Rb + r of band q and lags r steps behind warp 0; one __syncthreads per step -- but
+// every warp walks its own sequence "for each (image, band): for each column" instead of decoding a
+// flat step counter: all per-row decisions (row 0, pull from the ring, push to the ring, output
+// offsets) are taken once per row, and the loop over the columns carries only running indices.  Every
+// warp executes the same number of barriers (idle steps where it has no cell).
+//
+// Everything that arrives asynchronously from global memory (the staged inputs, ring blocks, blocks
+// of the state record) is requested TWO steps before the cell that uses it and lands in one of three
+// rotating buffers; a step ends with cp.async.wait_group 1, i.e. it waits for the copies issued one
+// step earlier, never for its own.  (With one step of lead and two buffers the wait at the end of a
+// step was for copies issued at its start, and a step is shorter than a trip to HBM on this part:
+// removing the wait altogether gained 9 % in the forward and 10 % in the backward kernel.)  Blocks
+// handed from warp to warp inside the CTA keep two parities.  A band boundary must therefore be
+// written at least two steps before the band below reads it: the plan keeps Rb <= W - 2.
 #pragma once
 
 #include "sweep_bwd.cuh"
 
 namespace m2d {
 
-// With STORE_HS (the backward's recompute sweep, CB = 1) every fresh state block also goes to the state
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_prev() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+// With STORE_HS (the backward's recompute sweep) every fresh state block also goes to the state
 // record a.hs and d_C is accumulated, and nothing is written to y.
-template <typename io_t, bool VEC, bool STORE_HS, int CB>
-__device__ __forceinline__ void forward_rows(const ScanArgs& a, float4* handoff, const float4* params, float D_own,
+template <typename io_t, bool VEC, bool STORE_HS>
+__device__ __forceinline__ void forward_rows(const ScanArgs& a, float4* smem, const float4* params, float D_own,
                                              int img0, int img_stride, int nb) {
     constexpr int HB = HsBlock<io_t>::f4;
-    constexpr int SP = 2 * CB * kSlotF4;         // float4 per hand-off slot (two parities x CB cells)
-    constexpr int PO = CB * kSlotF4;             // float4 between the two parities of a slot
-    constexpr int SO = CB * kStageBytes;         // bytes between the two parities of a stage
+    constexpr int PO = kSlotF4;                  // float4 between the two parities of a hand-off slot
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
     const int cq = lane >> 2, nq = lane & 3;
     const int g = blockIdx.y;
     const int ch0 = g * kGroup + cq * 4, n0 = nq * 4;
     const int chv = min(4, max(0, a.E - ch0));
     const int nv = min(4, max(0, a.N - n0));
     const int W = a.W, H = a.H, E = a.E, Rb = a.Rb, nbands = a.nbands;
-    const int nch = (W + CB - 1) / CB;           // chunks of CB columns per row
     const int pBT = (int)a.pBT, pBL = (int)a.pBL, pC = (int)a.pC;
     float4* const ring = a.ring + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * W) * kSlotF4 + lane;
-    float4* const my = handoff + r * SP + lane;  // read slot r, write slot r+1 (= my + SP)
-    char* const stage = reinterpret_cast<char*>(handoff + ((blockDim.x >> 5) + 1) * SP) + r * 2 * CB * kStageBytes;
+    float4* const pullbuf = smem + lane;                                  // warp 0: blocks of the row above the band
+    float4* const out = smem + 3 * kSlotF4 + r * 2 * kSlotF4 + lane;      // this row's states, for the warp below
+    const float4* const in = out - 2 * kSlotF4;                           // the row above (r > 0)
+    char* const stage = reinterpret_cast<char*>(smem + rows_handoff_f4(nwarps)) + r * 3 * kStageBytes;
     const bool y_lane = (g * kGroup + lane) < E;
     const bool ch_copier = (nq == 0) && (chv > 0);
     const bool st_copier = (cq == 0) && (nv > 0);
@@ -58,16 +68,17 @@ __device__ __forceinline__ void forward_rows(const ScanArgs& a, float4* handoff,
         aL2r[c][0] = pL4.x; aL2r[c][1] = pL4.y; aL2r[c][2] = pL4.z; aL2r[c][3] = pL4.w;
     }
 
-    // parity of the current step: stage / slot halves written now (po, so) and read now (po ^ PO,
-    // so ^ SO).  Every warp takes part in every step from the first one on (idle steps included), so
-    // all warps toggle in lock step from the same start value.
-    int po = PO;
-    int so = SO;
+    // Every warp takes part in every step from the first one on (idle steps included), so all warps
+    // rotate in lock step.  po: parity of the hand-off slots written in this step (read: po ^ PO).
+    // k3: which of the three asynchronous buffers is filled in this step, for the cell two steps on;
+    // the cell of this step reads buffer k3 + 1 (mod 3), filled two steps ago.
+    int po = PO, k3 = 0;
     auto end_step = [&]() {
-        cp_async_wait_all();
+        cp_async_commit();
+        cp_async_wait_prev();
         __syncthreads();
         po ^= PO;
-        so ^= SO;
+        k3 = (k3 == 2) ? 0 : k3 + 1;
     };
 
     struct Row { bool has, row0, pull, push; int pix0; float4* hs0; };
@@ -84,33 +95,27 @@ __device__ __forceinline__ void forward_rows(const ScanArgs& a, float4* handoff,
         return w;
     };
 
-    // stage the inputs (and the ring block above, for the first row of a band) of chunk c of row w
-    auto stage_chunk = [&](const Row& w, int c) {
-#pragma unroll
-        for (int cc = 0; cc < CB; ++cc) {
-            const int col = c * CB + cc;
-            if (CB == 1 || col < W) {
-                const int pix = w.pix0 + dir * col;
-                char* stg = stage + so + cc * kStageBytes;
-                if (VEC) {
-                    lc.issue_plain(smem_u32(stg), lane, pix, E);
-                } else {
-                    const int e0 = pix * E + ch0;
-                    stage4<VEC>(ch_copier, stg + cq * 16, static_cast<const io_t*>(a.x), e0, chv);
-                    stage4<VEC>(ch_copier, stg + (8 + cq) * 16, static_cast<const io_t*>(a.dT), e0, chv);
-                    stage4<VEC>(ch_copier, stg + (16 + cq) * 16, static_cast<const io_t*>(a.dL), e0, chv);
-                    if (STORE_HS) stage4<VEC>(ch_copier, stg + (24 + cq) * 16, static_cast<const io_t*>(a.gy), e0, chv);
-                    stage4<VEC>(st_copier, stg + (32 + nq) * 16, static_cast<const io_t*>(a.BT), pix * pBT + n0, nv);
-                    stage4<VEC>(st_copier, stg + (36 + nq) * 16, static_cast<const io_t*>(a.BL), pix * pBL + n0, nv);
-                    stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), pix * pC + n0, nv);
-                }
-                if (w.pull) cp_async_block(smem_u32(my + po + cc * kSlotF4), ring + col * kSlotF4, false);
-            }
+    // request the inputs (and the ring block above, for the first row of a band) of cell (w, col)
+    auto stage_cell = [&](const Row& w, int col) {
+        const int pix = w.pix0 + dir * col;
+        char* stg = stage + k3 * kStageBytes;
+        if (VEC) {
+            lc.issue_plain(smem_u32(stg), lane, pix, E);
+        } else {
+            const int e0 = pix * E + ch0;
+            stage4<VEC>(ch_copier, stg + cq * 16, static_cast<const io_t*>(a.x), e0, chv);
+            stage4<VEC>(ch_copier, stg + (8 + cq) * 16, static_cast<const io_t*>(a.dT), e0, chv);
+            stage4<VEC>(ch_copier, stg + (16 + cq) * 16, static_cast<const io_t*>(a.dL), e0, chv);
+            if (STORE_HS) stage4<VEC>(ch_copier, stg + (24 + cq) * 16, static_cast<const io_t*>(a.gy), e0, chv);
+            stage4<VEC>(st_copier, stg + (32 + nq) * 16, static_cast<const io_t*>(a.BT), pix * pBT + n0, nv);
+            stage4<VEC>(st_copier, stg + (36 + nq) * 16, static_cast<const io_t*>(a.BL), pix * pBL + n0, nv);
+            stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), pix * pC + n0, nv);
         }
+        if (w.pull) cp_async_block(smem_u32(pullbuf + k3 * kSlotF4), ring + col * kSlotF4, false);
     };
 
-    // one cell: reads the halves staged / handed over during the previous step, writes this step's
-    auto cell = [&](auto tag, const Row& w, const int cc, const int col) {
+    // one cell: reads what was requested two steps ago and what the warp above wrote in the previous step
+    auto cell = [&](auto tag, const Row& w, const int col) {
         constexpr bool INTERIOR = decltype(tag)::value;
         float wT, wL, offT, offL;
         if (INTERIOR) {
@@ -122,13 +127,15 @@ __device__ __forceinline__ void forward_rows(const ScanArgs& a, float4* handoff,
             offT = w.row0 ? ninf : (first ? 0.f : -1.f);
             offL = first ? ninf : (w.row0 ? 0.f : -1.f);
         }
+        const int rd = (k3 == 2) ? 0 : k3 + 1;
+        const float4* const tsrc = (r == 0) ? pullbuf + rd * kSlotF4 : in + (po ^ PO);
         float4 top[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            top[k] = my[(po ^ PO) + cc * kSlotF4 + k * 32];
+            top[k] = tsrc[k * 32];
             if (!INTERIOR && w.row0) top[k] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        const char* stg = stage + (so ^ SO) + cc * kStageBytes;
+        const char* stg = stage + rd * kStageBytes;
         const float4 vx = unstage4<io_t>(stg + cq * 16);
         const float4 vdT = unstage4<io_t>(stg + (8 + cq) * 16);
         const float4 vdL = unstage4<io_t>(stg + (16 + cq) * 16);
@@ -184,7 +191,7 @@ __device__ __forceinline__ void forward_rows(const ScanArgs& a, float4* handoff,
         {
             const float4 h0 = make_float4(h[0][0], h[0][1], h[0][2], h[0][3]), h1 = make_float4(h[1][0], h[1][1], h[1][2], h[1][3]);
             const float4 h2 = make_float4(h[2][0], h[2][1], h[2][2], h[2][3]), h3 = make_float4(h[3][0], h[3][1], h[3][2], h[3][3]);
-            float4* dst = my + SP + po + cc * kSlotF4;
+            float4* dst = out + po;
             dst[0] = h0; dst[32] = h1; dst[64] = h2; dst[96] = h3;
             if (w.push) stcg4_if(true, ring + col * kSlotF4, h0, h1, h2, h3);
             if (STORE_HS) {
@@ -219,10 +226,14 @@ __device__ __forceinline__ void forward_rows(const ScanArgs& a, float4* handoff,
     };
 
     // ---- the warp's sequence ---------------------------------------------------------------------
-    for (int k = 0; k < r; ++k) end_step();                  // idle until this warp's first step
+    // r idle steps, two steps that only request the first two cells, W steps per (image, band) item,
+    // Rb-1-r idle steps; in every step with a cell, the cell two columns on is requested first
+    for (int k = 0; k < r; ++k) end_step();
     int bi = 0, q = 0;
     Row cur = make_row(0, 0);
-    if (cur.has) stage_chunk(cur, 0);                         // the step that only stages
+    if (cur.has) stage_cell(cur, 0);
+    end_step();
+    if (cur.has) stage_cell(cur, 1);
     end_step();
     const int items = nb * nbands;
     for (int m = 0; m < items; ++m) {
@@ -233,40 +244,36 @@ __device__ __forceinline__ void forward_rows(const ScanArgs& a, float4* handoff,
             for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int n = 0; n < 4; ++n) h[c][n] = 0.f;    // a row starts from no left neighbour
-            for (int c = 0; c < nch; ++c) {
-                if (c + 1 < nch) stage_chunk(cur, c + 1);
-                else if (nxt.has) stage_chunk(nxt, 0);
-#pragma unroll
-                for (int cc = 0; cc < CB; ++cc) {
-                    const int col = c * CB + cc;
-                    if (CB == 1 || col < W) {
-                        if (cur.row0 || col == 0) cell(std::false_type{}, cur, cc, col);
-                        else cell(std::true_type{}, cur, cc, col);
-                    }
-                }
+            for (int col = 0; col < W; ++col) {
+                if (col + 2 < W) stage_cell(cur, col + 2);
+                else if (nxt.has) stage_cell(nxt, col + 2 - W);
+                if (cur.row0 || col == 0) cell(std::false_type{}, cur, col);
+                else cell(std::true_type{}, cur, col);
                 end_step();
             }
         } else {
-            for (int c = 0; c + 1 < nch; ++c) end_step();
-            if (nxt.has) stage_chunk(nxt, 0);
+            for (int col = 0; col + 2 < W; ++col) end_step();
+            if (nxt.has) stage_cell(nxt, 0);
+            end_step();
+            if (nxt.has) stage_cell(nxt, 1);
             end_step();
         }
         cur = nxt;
     }
     for (int k = 0; k < Rb - 1 - r; ++k) end_step();          // until the last warp is done
+    cp_async_wait_all();                                      // (only empty groups can be pending here)
 }
 
-// Adjoint sweep of one CTA over image b, batch mode, written as nested loops: same algorithm, layout
-// and barriers as reverse_sweep in sweep_bwd.cuh.  Bands are visited last to first, the bottom row of
+// Adjoint sweep of one CTA over image b, batch mode, written as nested loops: same algorithm and
+// data layout as reverse_sweep in sweep_bwd.cuh.  Bands are visited last to first, the bottom row of
 // a band leads (rank rr = Rb-1-r), columns run right to left.  Every warp executes the same number
-// of barriers: rr steps before its first staging step (the last of them fetches the right-most state
-// block of its first row for the warp below), one step that only stages, W steps per band, and
-// Rb-1-rr idle steps at the end.
+// of barriers: rr + 2 steps before its first cell (the last three of them request, in this order, the
+// right-most state block of its first row for the warp below, cell W-1 and cell W-2), W steps per
+// band, and Rb-1-rr idle steps at the end.
 template <typename io_t, bool VEC>
-__device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff, const float4* params, float D_own,
+__device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* smem, const float4* params, float D_own,
                                              float (&dAT)[4][4], float (&dAL)[4][4], float (&dD)[4], int b) {
-    constexpr int PO = kSlotF4;               // float4 between the two parities of a slot / h area
-    constexpr int SO = kStageBytes;           // bytes between the two parities of a stage
+    constexpr int PO = kSlotF4;               // float4 between the two parities of a hand-off slot
     constexpr int HB = HsBlock<io_t>::f4;     // float4 units per state-record block
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
@@ -280,11 +287,13 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
     const int pBT = (int)a.pBT, pBL = (int)a.pBL, pC = (int)a.pC;
     const int dir = a.dir;
     float4* const ring = a.ring + ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * W) * kSlotF4 + lane;
-    float4* const my = handoff + rr * kSlotPair + lane;                       // pT: read slot rr, write slot rr+1
-    char* const stage = reinterpret_cast<char*>(handoff + (nwarps + 1) * kSlotPair) + r * 2 * kStageBytes;
-    float4* const harea = reinterpret_cast<float4*>(reinterpret_cast<char*>(handoff) + sweep_smem_bytes(nwarps)) + lane;
-    float4* const h_own = harea + (r + 1) * kSlotPair;                        // this row's h[i][j-1]
-    float4* const h_up = harea + r * kSlotPair;                               // the row above: h[i-1][j]
+    float4* const pullbuf = smem + lane;                                      // rank 0: pT of the row below the band
+    float4* const out = smem + 3 * kSlotF4 + rr * 2 * kSlotF4 + lane;         // pT of this row, for the row above
+    float4* const in = out - 2 * kSlotF4;                                     // pT of the row below (rr > 0)
+    char* const stage = reinterpret_cast<char*>(smem + rows_handoff_f4(nwarps)) + r * 3 * kStageBytes;
+    float4* const harea = reinterpret_cast<float4*>(reinterpret_cast<char*>(smem) + rows_fwd_smem_bytes(nwarps)) + lane;
+    float4* const h_own = harea + (r + 1) * 3 * kSlotF4;                      // this row's h[i][j-1]
+    float4* const h_up = harea + r * 3 * kSlotF4;                             // the row above: h[i-1][j]
     const float4* const hs_img = a.hs + ((size_t)b * groups + g) * H * W * HB + lane;
     const bool y_lane = (g * kGroup + lane) < E;
     const bool ch_copier = (nq == 0) && (chv > 0);
@@ -311,12 +320,15 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
         return area[c * 32];
     };
 
-    int po = PO, so = SO;                      // halves written in the current step; read: po ^ PO, so ^ SO
+    // po: parity of the hand-off slots written in this step (read: po ^ PO); k3: which of the three
+    // asynchronous buffers is filled in this step, for the cell two steps on (read: k3 + 1 mod 3)
+    int po = PO, k3 = 0;
     auto end_step = [&]() {
-        cp_async_wait_all();
+        cp_async_commit();
+        cp_async_wait_prev();
         __syncthreads();
         po ^= PO;
-        so ^= SO;
+        k3 = (k3 == 2) ? 0 : k3 + 1;
     };
 
     // row of band q owned by this warp; pixR = memory pixel of its right-most cell (i, W-1)
@@ -333,14 +345,15 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
         w.pixR = scan_pixel(a, b, w.i, W - 1);
         return w;
     };
-    // fetch h[i][W-1] of row w for the warp below (nobody's left neighbour, so no warp stages it otherwise)
+    // request h[i][W-1] of row w for the warp below (nobody's left neighbour, so no cell's request covers it)
     auto prefetch_row_end = [&](const Row& w) {
-        if (feeds_below && w.has) copy_block(smem_u32(h_own + po), hs_img + ((size_t)w.i * W + (W - 1)) * HB);
+        if (feeds_below && w.has) copy_block(smem_u32(h_own + k3 * kSlotF4), hs_img + ((size_t)w.i * W + (W - 1)) * HB);
     };
-    // stage the inputs, h[i][j-1], for the top row of a band h[i-1][j], for the bottom row pT of the band below
+    // request for cell (w, j): the inputs, h[i][j-1], for the top row of a band h[i-1][j], for the bottom
+    // row of a band pT of the band below
     auto stage_cell = [&](const Row& w, int j) {
         const int pix = w.pixR - dir * (W - 1 - j);
-        char* stg = stage + so;
+        char* stg = stage + k3 * kStageBytes;
         if (VEC) {
             lc.issue_plain(smem_u32(stg), lane, pix, E);
         } else {
@@ -354,9 +367,9 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
             stage4<VEC>(st_copier, stg + (40 + nq) * 16, static_cast<const io_t*>(a.C), pix * pC + n0, nv);
         }
         const float4* ph = hs_img + ((size_t)w.i * W + (j - 1)) * HB;            // h[i][j-1]
-        if (j > 0) copy_block(smem_u32(h_own + po), ph);
-        if (w.top) copy_block(smem_u32(h_up + po), ph + (ptrdiff_t)(1 - W) * HB);   // h[i-1][j]
-        if (w.pull) cp_async_block(smem_u32(my + po), ring + j * kSlotF4, false);
+        if (j > 0) copy_block(smem_u32(h_own + k3 * kSlotF4), ph);
+        if (w.top) copy_block(smem_u32(h_up + k3 * kSlotF4), ph + (ptrdiff_t)(1 - W) * HB);   // h[i-1][j]
+        if (w.pull) cp_async_block(smem_u32(pullbuf + k3 * kSlotF4), ring + j * kSlotF4, false);
     };
 
     auto cell = [&](auto tag, const Row& w, const int j) {
@@ -376,7 +389,11 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
           offL = first ? ninf : 0.f;
       }
       const float2 offT2 = make_float2(offT, offT), offL2 = make_float2(offL, offL);
-      const char* stg = stage + (so ^ SO);
+      const int rd = (k3 == 2) ? 0 : k3 + 1;
+      const char* stg = stage + rd * kStageBytes;
+      const float4* const hl_src = h_own + rd * kSlotF4;
+      const float4* const ht_src = h_up + rd * kSlotF4;
+      const float4* const pd_src = (rr == 0) ? pullbuf + rd * kSlotF4 : in + (po ^ PO);
       const float4 vx = unstage4<io_t>(stg + cq * 16);
       const float4 vdT = unstage4<io_t>(stg + (8 + cq) * 16);
       const float4 vdL = unstage4<io_t>(stg + (16 + cq) * 16);
@@ -397,9 +414,9 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
       float o_dT[4], o_dL[4], o_dx[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-          const float4 hl4 = (INTERIOR || j > 0) ? block_states(h_own + (po ^ PO), c) : zero4;
-          const float4 ht4 = (INTERIOR || !w.row0) ? block_states(h_up + (po ^ PO), c) : zero4;
-          const float4 pd4 = my[(po ^ PO) + c * 32];
+          const float4 hl4 = (INTERIOR || j > 0) ? block_states(hl_src, c) : zero4;
+          const float4 ht4 = (INTERIOR || !w.row0) ? block_states(ht_src, c) : zero4;
+          const float4 pd4 = pd_src[c * 32];
           const float hls[4] = {hl4.x, hl4.y, hl4.z, hl4.w};
           const float hts[4] = {ht4.x, ht4.y, ht4.z, ht4.w};
           const float pds[4] = {pd4.x, pd4.y, pd4.z, pd4.w};
@@ -438,7 +455,7 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
           }
           // pT goes to the row above: next rank's slot, and the ring when that row is in another band
           const float4 pT4 = make_float4(pt[0], pt[1], pt[2], pt[3]);
-          my[kSlotPair + po + c * 32] = pT4;
+          out[po + c * 32] = pT4;
           if (w.push) __stcg(ring + j * kSlotF4 + c * 32, pT4);
           const float qT = qT2.x + qT2.y, qL = qL2.x + qL2.y, sT = sT2.x + sT2.y, sL = sL2.x + sL2.y;
           if (INTERIOR) {
@@ -493,7 +510,9 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
         prefetch_row_end(cur);
         end_step();
     }
-    if (cur.has) stage_cell(cur, W - 1);                      // the step that only stages
+    if (cur.has) stage_cell(cur, W - 1);
+    end_step();
+    if (cur.has) stage_cell(cur, W - 2);
     end_step();
     for (int q = nbands - 1; q >= 0; --q) {
         const Row nxt = make_row(q - 1);                      // (.has is false past the last item)
@@ -503,18 +522,23 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
 #pragma unroll
                 for (int n = 0; n < 4; ++n) pL[c][n] = 0.f;   // a row starts from no right neighbour
             if (cur.bottom) {
-                // the bottom row of the map has no row below: nobody fills this rank's incoming slot during
-                // the row, so it is cleared once and the cells read zeros from it
+                // the bottom row of the map has no row below: nothing arrives in this rank's incoming
+                // buffers during the row, so they are cleared once and the cells read zeros from them
+                if (rr == 0) {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) my[k * 32] = zero4;
+                    for (int k = 0; k < 12; ++k) pullbuf[k * 32] = zero4;
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) in[k * 32] = zero4;
+                }
             }
             for (int j = W - 1; j >= 0; --j) {
-                if (j > 0) {
-                    stage_cell(cur, j - 1);
-                    // cell (i, 0) has no left block: its slot is free for the right-most block of the next row
-                    if (j == 1 && nxt.has) prefetch_row_end(nxt);
+                if (j >= 2) {
+                    stage_cell(cur, j - 2);
+                    // cell (i, 0) has no left block: its buffer is free for the right-most block of the next row
+                    if (j == 2 && nxt.has) prefetch_row_end(nxt);
                 } else if (nxt.has) {
-                    stage_cell(nxt, W - 1);
+                    stage_cell(nxt, W - 2 + j);
                 }
                 if (cur.row0 || j == 0) cell(std::false_type{}, cur, j);
                 else cell(std::true_type{}, cur, j);
@@ -522,14 +546,17 @@ __device__ __forceinline__ void reverse_rows(const ScanArgs& a, float4* handoff,
             }
         } else {
             for (int j = W - 1; j >= 0; --j) {
-                if (j == 1 && nxt.has) prefetch_row_end(nxt);
-                if (j == 0 && nxt.has) stage_cell(nxt, W - 1);
+                if (nxt.has) {
+                    if (j == 2) prefetch_row_end(nxt);
+                    else if (j < 2) stage_cell(nxt, W - 2 + j);
+                }
                 end_step();
             }
         }
         cur = nxt;
     }
     for (int k = 0; k < Rb - 1 - rr; ++k) end_step();         // until the last warp is done
+    cp_async_wait_all();                                      // (only empty groups can be pending here)
 }
 
 }  // namespace m2d

@@ -59,6 +59,9 @@ FWD_SHAPES = [
     (1, 200, 136, 64, 16),  # large map, one image: many CTAs chained along the bands of the image
     (2, 96, 40, 32, 16),
     (1, 2400, 24, 32, 16),  # more bands than resident CTAs: the chain closes into a ring
+    (300, 13, 3, 32, 16),   # many narrow maps: batch mode with one row per band (a boundary is read two steps after it is written)
+    (300, 11, 4, 32, 16),   # ... two rows per band
+    (300, 20, 2, 32, 16),   # two columns: batch mode falls back to the flat step loop
 ]
 
 
@@ -111,6 +114,9 @@ BWD_SHAPES = [
     (1, 120, 72, 64, 16),   # large map, one image: chained CTAs in both sweeps of the backward
     (2, 96, 40, 32, 16),
     (1, 2000, 20, 32, 16),  # more bands than resident CTAs: the chain closes into a ring
+    (300, 13, 3, 32, 16),   # many narrow maps: batch mode with one row per band
+    (300, 11, 4, 32, 16),   # ... two rows per band
+    (300, 20, 2, 32, 16),   # two columns: batch mode falls back to the flat step loops
 ]
 
 
