@@ -211,7 +211,7 @@ def time_config2(dtype, dev, steps, warmup, world, sampler_index=None, e2e_steps
     # ---- end to end from pinned host buffers through the package's host-tensor API: every step copies
     # its inputs host -> device, runs forward + backward, and copies y and the nine gradients back;
     # copy-in, kernels and copy-out of consecutive calls overlap on three streams
-    pipe = HostScanPipeline(dev, depth=4)
+    pipe = HostScanPipeline(dev, depth=8)
     host_views = [{k: (hb if contig else hb.as_strided(shape, stride, off)) for k, (hb, shape, stride, off, contig) in h.items()}
                   for h in host]
     outs_host = [None] * len(host_views)

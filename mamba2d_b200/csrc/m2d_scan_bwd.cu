@@ -11,6 +11,9 @@
 #ifndef M2D_BWD_MAXW
 #define M2D_BWD_MAXW 6
 #endif
+#ifndef M2D_BWD_MINB
+#define M2D_BWD_MINB 2
+#endif
 
 namespace m2d {
 
@@ -165,7 +168,7 @@ __global__ void __launch_bounds__(M2D_BWD_MAXW * 32, 2) m2d_bwd_chained_kernel(c
 
 // Batch mode (one CTA per image and channel group): both sweeps written as nested loops.
 template <typename io_t, bool VEC>
-__global__ void __launch_bounds__(M2D_BWD_MAXW * 32, 2) m2d_bwd_kernel(const ScanArgs a) {
+__global__ void __launch_bounds__(M2D_BWD_MAXW * 32, M2D_BWD_MINB) m2d_bwd_kernel(const ScanArgs a) {
     extern __shared__ float4 smem[];
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
