@@ -78,6 +78,14 @@ int m2d_dtproj_bwd(const m2d_proj_desc *desc, void *stream);
  */
 int m2d_xproj_wgrad(const m2d_proj_desc *desc, void *stream);
 
+/*
+ * 1 if m2d_xproj_wgrad would run this problem on the tensor cores (bf16 operands staged by TMA,
+ * tcgen05.mma with an fp32 accumulator in tensor memory), 0 if on the CUDA cores (fp32; bf16 problems
+ * with E or proj_pitch not a multiple of 8, pointers not 16-byte aligned, more than 128 projection
+ * columns, or M2D_WGRAD_TC=0 in the environment).  Needs x and d_proj set; launches nothing.
+ */
+int m2d_xproj_wgrad_on_tensor_cores(const m2d_proj_desc *desc);
+
 #ifdef __cplusplus
 }
 #endif

@@ -20,7 +20,8 @@ NOALLOC_SCRATCH_BYTES = 32 << 20     # M2D_NOALLOC_SCRATCH_BYTES in include/m2d_
 EXPORTS = ("m2d_abi_version", "m2d_strerror", "m2d_scan_fwd_workspace", "m2d_scan_bwd_workspace",
            "m2d_scan_fwd", "m2d_scan_bwd", "m2d_scan_fwd_noalloc", "m2d_scan_fwd_noalloc_need", "m2d_scan_fwd_status_offset",
            "m2d_scan_bwd_status_offset", "m2d_scan_fwd_chain", "m2d_scan_bwd_chain", "m2d_scan_chain_bound",
-           "m2d_proj_workspace", "m2d_dtproj_fwd", "m2d_dtproj_bwd", "m2d_xproj_wgrad")
+           "m2d_proj_workspace", "m2d_dtproj_fwd", "m2d_dtproj_bwd", "m2d_xproj_wgrad",
+           "m2d_xproj_wgrad_on_tensor_cores")
 PROJ_MAX_E, PROJ_MAX_R = 640, 64     # M2D_PROJ_MAX_E / M2D_PROJ_MAX_R in include/m2d_proj.h
 
 
@@ -90,6 +91,8 @@ def lib():
         for name in ("m2d_dtproj_fwd", "m2d_dtproj_bwd", "m2d_xproj_wgrad"):
             getattr(L, name).restype = ctypes.c_int
             getattr(L, name).argtypes = [ctypes.POINTER(ProjDesc), ctypes.c_void_p]
+        L.m2d_xproj_wgrad_on_tensor_cores.restype = ctypes.c_int
+        L.m2d_xproj_wgrad_on_tensor_cores.argtypes = [ctypes.POINTER(ProjDesc)]
         if L.m2d_abi_version() != ABI_VERSION:
             raise RuntimeError(f"libm2d_scan.so has ABI {L.m2d_abi_version()}, expected {ABI_VERSION}")
         _LIB = L

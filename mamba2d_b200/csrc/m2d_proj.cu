@@ -13,6 +13,7 @@
 
 #include "common.cuh"
 #include "plan.cuh"
+#include "wgrad_tc.cuh"
 
 namespace m2d {
 
@@ -84,7 +85,7 @@ static ProjPlan plan_proj(const m2d_proj_desc* d) {
     if (slabs < 1) slabs = 1;
     p.rows_per_slab = (int)(((d->P + slabs - 1) / slabs + 31) / 32 * 32);
     p.slabs = (int)((d->P + p.rows_per_slab - 1) / p.rows_per_slab);
-    p.wg_partials = (size_t)p.slabs * p.K * d->E * sizeof(float);
+    p.wg_partials = align256((size_t)p.slabs * p.K * d->E * sizeof(float)) + 256;   // + the status word of the tensor-core kernel
     return p;
 }
 
@@ -561,9 +562,33 @@ static int dispatch_dt(const m2d_proj_desc* d, bool bwd, cudaStream_t st) {
     }
 }
 
+// bf16 operands: the tensor-core kernel, when the problem meets its alignment rules (otherwise, and for
+// fp32, whose 1e-4 bar rules out tf32 operands, the CUDA-core kernel below).  Returns -1 for "not taken".
+static int launch_wgrad_tc(const m2d_proj_desc* d, const ProjPlan& p, cudaStream_t st) {
+    const TcPlan t = tc_plan(d->P, d->E, p.K, d->proj_pitch, d->x, d->d_proj, p.slabs);
+    if (!t.ok) return -1;
+    CUtensorMap map_a, map_b;
+    if (!tc_make_map(&map_a, d->d_proj, d->P, p.K, d->proj_pitch) || !tc_make_map(&map_b, d->x, d->P, d->E, d->E)) return -1;
+    TcArgs a;
+    a.K = p.K; a.E = d->E; a.nbk = t.nbk; a.stages = t.stages; a.total_blocks = t.total_blocks; a.blocks_per_cta = t.blocks_per_cta;
+    a.partials = static_cast<float*>(d->workspace);
+    a.status = reinterpret_cast<int*>(static_cast<char*>(d->workspace) + p.wg_partials - 256);
+    if (cudaMemsetAsync(a.status, 0, sizeof(int), st) != cudaSuccess) return M2D_ERR_LAUNCH;
+    if (cudaFuncSetAttribute(xproj_wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t.smem) != cudaSuccess) return M2D_ERR_LAUNCH;
+    xproj_wgrad_tc_kernel<<<dim3(t.grid_x, t.ny), 128, t.smem, st>>>(map_a, map_b, a);
+    if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
+    const long long ke = (long long)p.K * d->E;
+    xproj_wgrad_finalize<__nv_bfloat16><<<(int)((ke + 31) / 32), dim3(32, 8), 0, st>>>(a.partials, t.grid_x, ke, static_cast<__nv_bfloat16*>(d->d_Wx));
+    return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
+}
+
 template <typename io_t>
 static int launch_wgrad(const m2d_proj_desc* d, cudaStream_t st) {
     const ProjPlan p = plan_proj(d);
+    if (sizeof(io_t) == 2) {
+        const int rc = launch_wgrad_tc(d, p, st);
+        if (rc >= 0) return rc;
+    }
     WgArgs a;
     a.P = (int)d->P; a.pitch = (int)d->proj_pitch; a.E = d->E; a.K = p.K; a.rows_per_slab = p.rows_per_slab;
     a.x = d->x; a.d_proj = d->d_proj;
@@ -611,6 +636,15 @@ extern "C" int m2d_dtproj_bwd(const m2d_proj_desc* d, void* stream) {
     if (!workspace_ok(d, plan_proj(d).dt_partials)) return M2D_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return d->dtype == M2D_F32 ? dispatch_dt<float>(d, true, st) : dispatch_dt<__nv_bfloat16>(d, true, st);
+}
+
+extern "C" int m2d_xproj_wgrad_on_tensor_cores(const m2d_proj_desc* d) {
+    if (check_proj(d) != M2D_OK || d->dtype != M2D_BF16 || !d->x || !d->d_proj) return 0;
+    const ProjPlan p = plan_proj(d);
+    const TcPlan t = tc_plan(d->P, d->E, p.K, d->proj_pitch, d->x, d->d_proj, p.slabs);
+    if (!t.ok) return 0;
+    CUtensorMap map_a, map_b;
+    return tc_make_map(&map_a, d->d_proj, d->P, p.K, d->proj_pitch) && tc_make_map(&map_b, d->x, d->P, d->E, d->E) ? 1 : 0;
 }
 
 extern "C" int m2d_xproj_wgrad(const m2d_proj_desc* d, void* stream) {

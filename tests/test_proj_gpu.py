@@ -143,3 +143,31 @@ def test_fused_softplus_is_accurate_over_its_whole_range():
     for got, ref in ((dT[0, 0, :, 5].double().cpu(), want), (dL[0, 0, :, 9].double().cpu(), want.flip(0))):
         rel = ((got - ref).abs() / ref.clamp_min(1e-30)).max()
         assert float(rel) < 1e-6
+
+
+@pytest.mark.parametrize("P,E,R", [(50176, 64, 4), (20000, 128, 8), (9999, 320, 20), (5000, 512, 32), (3000, 576, 36),
+                                   (777, 40, 4), (64, 64, 4), (65, 192, 12)])
+def test_xproj_weight_gradient_on_tensor_cores(P, E, R, monkeypatch):
+    """bf16 problems that meet the alignment rules run on tcgen05 (the library says so itself); the
+    result matches an fp64 product of the same bf16 operands and the CUDA-core kernel's."""
+    import ctypes
+    from mamba2d_b200 import _lib, wavefront_cuda as wc
+    N = 16
+    K = 2 * R + 3 * N
+    g = torch.Generator().manual_seed(P + E)
+    d_proj = torch.randn(P, K, generator=g).bfloat16().cuda()
+    x = torch.randn(P, E, generator=g).bfloat16().cuda()
+    monkeypatch.delenv("M2D_WGRAD_TC", raising=False)
+    d = wc._proj_desc(d_proj, E, R, N)
+    d.d_proj, d.x = d_proj.data_ptr(), x.data_ptr()
+    assert _lib.lib().m2d_xproj_wgrad_on_tensor_cores(ctypes.byref(d)) == 1
+    got = wc._xproj_wgrad(d_proj, x, N, R)
+    torch.cuda.synchronize()
+    want = d_proj.double().T @ x.double()
+    scale = float(want.abs().max())
+    assert float((got.double() - want).abs().max()) <= 2e-2 * scale
+    monkeypatch.setenv("M2D_WGRAD_TC", "0")
+    assert _lib.lib().m2d_xproj_wgrad_on_tensor_cores(ctypes.byref(d)) == 0
+    simt = wc._xproj_wgrad(d_proj, x, N, R)
+    torch.cuda.synchronize()
+    assert float((got.double() - simt.double()).abs().max()) <= 1e-2 * scale     # both round their fp32 sums to bf16
