@@ -50,8 +50,8 @@ BYTES = {"f32": 4, "bf16": 2}
 
 # DRAM bytes (read + write) of ONE launch of the dominant kernel, from an ncu capture of this same
 # workload; see profiles/ for the capture summaries.  None = not captured for that dtype.
-NCU_TRAFFIC = {"f32": 6.093e9, "bf16": 3.711e9}
-NCU_TRAFFIC_FROM = "c9ff62d"  # the commit whose kernels were captured
+NCU_TRAFFIC = {"f32": 6.064e9, "bf16": 3.696e9}
+NCU_TRAFFIC_FROM = "538d212"  # the commit whose kernels were captured
 
 
 def fwd_bytes(D, HW, s, B=BATCH, N=NSTATE):
