@@ -481,7 +481,7 @@ def m2dt_images_per_s(dev, world, batch=128, iters=5, variants=None):
         return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
 
-def m2ds_train_step(dev, world, local, global_batch=1024, micro_batch=128, steps=2, warmup=1):
+def m2ds_train_step(dev, world, local, global_batch=1024, micro_batch=128, steps=2, warmup=2):
     """Config 4: one training step of the reference's unchanged M2D-S classifier (blocks [3,12,14,3],
     widths [96,192,384,576]) on top of this op: forward + backward + AdamW with the reference's
     parameter groups, cross-entropy on uniform random labels, bf16 autocast, global batch 1024 split
