@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(128, 1) xproj_wgrad_tc_kernel(const __grid_con
     }
 
     // ---- epilogue: thread (warp, lane) owns accumulator row 32*warp + lane ----
-    // (the verdict is taken CTA-wide: tcgen05.ld below must be executed by whole warps together)
+    // (the decision is taken CTA-wide: tcgen05.ld below must be executed by whole warps together)
     const bool have = __syncthreads_and(mbar_wait(done_bar, 0u, abort) ? 1 : 0) != 0;
     tc_fence_after();
     const int row = warp * 32 + lane;
