@@ -517,13 +517,29 @@ static ProjArgs proj_args(const m2d_proj_desc* d, const ProjPlan& p) {
     return a;
 }
 
+// CTAs per direction: the grid (gx, 2 directions) fills the resident CTA slots of the device exactly
+// once, so that every SM gets the same number of CTAs and every CTA the same number of tiles (with the
+// planned 2 x SMs per direction some SMs held five CTAs and others three: a quarter of the kernel was
+// spent waiting for the fuller ones).  Never more than the plan's gx, which sized the workspace.
+template <typename K>
+static int balanced_gx(K kern, const ProjPlan& p, size_t smem) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, p.threads, smem) != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        return p.gx;
+    }
+    const int gx = per_sm * sm_count() / 2;
+    return gx < 1 ? 1 : (gx < p.gx ? gx : p.gx);
+}
+
 template <typename io_t, int RB>
 static int launch_dt_fwd(const ProjArgs& a, const ProjPlan& p, cudaStream_t st) {
     const size_t smem = (size_t)p.TP * RB * sizeof(float);
-    if (p.threads <= 256) dtproj_fwd_kernel<io_t, RB, 256><<<dim3(p.gx, 2), p.threads, smem, st>>>(a);
-    else if (p.threads <= 384) dtproj_fwd_kernel<io_t, RB, 384><<<dim3(p.gx, 2), p.threads, smem, st>>>(a);
-    else if (p.threads <= 512) dtproj_fwd_kernel<io_t, RB, 512><<<dim3(p.gx, 2), p.threads, smem, st>>>(a);
-    else dtproj_fwd_kernel<io_t, RB, M2D_PROJ_MAX_E><<<dim3(p.gx, 2), p.threads, smem, st>>>(a);
+    auto kern = p.threads <= 256   ? dtproj_fwd_kernel<io_t, RB, 256>
+                : p.threads <= 384 ? dtproj_fwd_kernel<io_t, RB, 384>
+                : p.threads <= 512 ? dtproj_fwd_kernel<io_t, RB, 512>
+                                   : dtproj_fwd_kernel<io_t, RB, M2D_PROJ_MAX_E>;
+    kern<<<dim3(balanced_gx(kern, p, smem), 2), p.threads, smem, st>>>(a);
     return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
 }
 
@@ -540,10 +556,11 @@ static int launch_dt_bwd(const m2d_proj_desc* d, const ProjArgs& a, const ProjPl
                                    : dtproj_bwd_kernel<io_t, RB, M2D_PROJ_MAX_E>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return M2D_ERR_LAUNCH;
-    kern<<<dim3(p.gx, 2), p.threads, smem, st>>>(a);
+    const int gx = balanced_gx(kern, p, smem);
+    kern<<<dim3(gx, 2), p.threads, smem, st>>>(a);
     if (cudaGetLastError() != cudaSuccess) return M2D_ERR_LAUNCH;
     const int n = 2 * (RB + 1) * p.EB;
-    dtproj_bwd_finalize<io_t><<<(n + 31) / 32, dim3(32, 8), 0, st>>>(a.partials, p.gx, RB, p.EB, d->E, d->R,
+    dtproj_bwd_finalize<io_t><<<(n + 31) / 32, dim3(32, 8), 0, st>>>(a.partials, gx, RB, p.EB, d->E, d->R,
                                                              static_cast<io_t*>(d->d_WT), static_cast<io_t*>(d->d_WL),
                                                              static_cast<io_t*>(d->d_bT), static_cast<io_t*>(d->d_bL));
     return cudaGetLastError() == cudaSuccess ? M2D_OK : M2D_ERR_LAUNCH;
